@@ -1,0 +1,14 @@
+// Instantiations of the fused AllReduce kernel: four ranks, two-shot, NVFP4 and producer-pushed input.
+#include "ar_table.h"
+namespace fp4ar {
+void ar_register_p4b(ArKernelEntry* out, int* n) {
+  out[(*n)++] = make_entry<4, 1, 1, 0>();
+  out[(*n)++] = make_entry<4, 1, 1, 1>();
+  out[(*n)++] = make_entry<4, 1, 1, 2>();
+  out[(*n)++] = make_entry<4, 1, 1, 3>();
+  out[(*n)++] = make_entry<4, 1, 2, 0>();
+  out[(*n)++] = make_entry<4, 1, 2, 1>();
+  out[(*n)++] = make_entry<4, 1, 2, 2>();
+  out[(*n)++] = make_entry<4, 1, 2, 3>();
+}
+}  // namespace fp4ar

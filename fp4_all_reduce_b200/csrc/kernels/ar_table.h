@@ -1,0 +1,36 @@
+// Table of compiled fused-kernel shapes.  Each ar_inst_*.cu translation unit instantiates a slice of
+// the (P, algorithm, input, epilogue) space and registers it here; the runtime looks shapes up by key.
+#pragma once
+#include "ar_kernel.cuh"
+
+namespace fp4ar {
+
+struct ArKernelEntry {
+  int P, algo, input, epi, T;
+  const void* fn;
+  int team_bytes, cta_extra, max_teams;
+};
+
+constexpr int kTeamWarps = 2;   // warps per row team in every compiled shape
+
+template <int P, int ALGO, int IN, int EPI>
+inline ArKernelEntry make_entry() {
+  using S = ArShape<P, ALGO, IN, EPI, kTeamWarps>;
+  ArKernelEntry e;
+  e.P = P; e.algo = ALGO; e.input = IN; e.epi = EPI; e.T = kTeamWarps;
+  e.fn = reinterpret_cast<const void*>(&ar_kernel<P, ALGO, IN, EPI, kTeamWarps>);
+  e.team_bytes = S::kTeamBytes; e.cta_extra = S::kCtaExtra; e.max_teams = S::kMaxTeams;
+  return e;
+}
+
+// Defined once per instantiation unit; each appends its entries.
+void ar_register_p1(ArKernelEntry* out, int* n);
+void ar_register_p2(ArKernelEntry* out, int* n);
+void ar_register_p2b(ArKernelEntry* out, int* n);
+void ar_register_p4(ArKernelEntry* out, int* n);
+void ar_register_p4b(ArKernelEntry* out, int* n);
+void ar_register_p8(ArKernelEntry* out, int* n);
+void ar_register_p8b(ArKernelEntry* out, int* n);
+void ar_register_cmp(ArKernelEntry* out, int* n);
+
+}  // namespace fp4ar

@@ -1,0 +1,462 @@
+// Stand-alone single-GPU kernels built from the same codec primitives as the fused AllReduce:
+// row encode (dynamic row scale or static per-tensor scale), rank-ordered decode-sum, the two-shot
+// owner step (decode-sum + re-encode + decode of the re-encoding), add + Gemma RMSNorm with BF16 /
+// NVFP4 / MXFP8 output, and the sentinel fill of a receive window.
+//
+// All of them stream 12 KB rows: one warp per row, rows brought into shared memory by bulk
+// asynchronous copies where the access pattern would otherwise be 64 B per lane, BF16 results staged
+// in shared memory and written back with one bulk store per row.
+//
+// Reference project counterparts: bench/codec/codec_bench.cu:139-590 (k_enc_*, k_dec_*, k_ts_*),
+// kernels/push/tp2_l2.cu:967-978 (fill_sentinel), bench/fused_norm/drv_norm.cu:75-123 (ref_norm).
+#include "../include/fp4ar.h"
+#include "../include/fp4ar_codec.cuh"
+#include "../include/fp4ar_async.cuh"
+#include "host_util.h"
+
+namespace fp4ar {
+
+constexpr int kRowB = kHidden * 2;
+constexpr int kOpsWarps = 6;     // warps per CTA; each owns 36 KB of shared memory
+
+__device__ __forceinline__ void perm4(uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d, int f) {
+  if (f & 1) { uint32_t t = a; a = b; b = t; t = c; c = d; d = t; }
+  if (f & 2) { uint32_t t = a; a = c; c = t; t = b; b = d; d = t; }
+}
+
+// Bounded wait on a row load; a failure only flags the error word (the op's output is then undefined).
+__device__ __forceinline__ void wait_row(uint64_t* bar, uint32_t parity, uint32_t* err) {
+  if (mbar_test(bar, parity)) return;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t n = 0;
+  while (!mbar_test(bar, parity)) {
+    if ((++n & 63u) == 0u && global_timer_ns() - t0 > 2000000000ull) { atomicExch(err, 1u); return; }
+  }
+}
+
+struct WarpSmem {
+  uint8_t* a;      // 12 KB row buffer
+  uint8_t* b;      // 12 KB row buffer
+  uint8_t* o;      // 12 KB output staging
+  uint64_t* bar;   // 2 mbarriers
+};
+__device__ __forceinline__ WarpSmem carve(uint8_t* smem, int warp) {
+  WarpSmem w;
+  uint8_t* base = smem + (size_t)warp * (3 * kRowB + 64);
+  w.a = base; w.b = base + kRowB; w.o = base + 2 * kRowB;
+  w.bar = reinterpret_cast<uint64_t*>(base + 3 * kRowB);
+  return w;
+}
+constexpr int kOpsSmem = kOpsWarps * (3 * kRowB + 64);
+
+// Encode the BF16 row sitting in shared memory at `xrow`; lane l handles pairs l + 32 j.
+// Writes canonical 16 B value groups and 2 B scale pairs through the two callbacks.
+template <class PutQ, class PutS>
+__device__ __forceinline__ void encode_row_from_smem(const uint8_t* xrow, int lane, float inv_fixed, bool use_fixed,
+                                                     float& rs_out, PutQ put_q, PutS put_s) {
+  const int f = (lane >> 1) & 3;
+  uint32_t bmp[6];
+  float am = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 6; j++) {
+    const int p = lane + 32 * j;
+    const __nv_bfloat162 z2 = __floats2bfloat162_rn(0.0f, 0.0f);
+    __nv_bfloat162 ma = z2, mb = z2;
+    ma = chunk_absmax(lds16(xrow + p * 64 + ((0 ^ f) << 4)), ma);
+    ma = chunk_absmax(lds16(xrow + p * 64 + ((1 ^ f) << 4)), ma);
+    mb = chunk_absmax(lds16(xrow + p * 64 + ((2 ^ f) << 4)), mb);
+    mb = chunk_absmax(lds16(xrow + p * 64 + ((3 ^ f) << 4)), mb);
+    const uint32_t xa = bf16x2_hmax_bits(ma), xb = bf16x2_hmax_bits(mb);
+    bmp[j] = (f & 2) ? (xb | (xa << 16)) : (xa | (xb << 16));
+    am = fmaxf(am, __uint_as_float(max(xa, xb) << 16));
+  }
+  am = warp_max(am);
+  const RowScale sc = row_scale_from_amax(am);
+  const float inv = use_fixed ? inv_fixed : sc.inv;
+  rs_out = sc.rs;
+#pragma unroll
+  for (int j = 0; j < 6; j++) {
+    const int p = lane + 32 * j;
+    const float bm0 = __uint_as_float(bmp[j] << 16), bm1 = __uint_as_float(bmp[j] & 0xffff0000u);
+    float m0, m1;
+    const uint32_t sf2 = pair_block_scales(bm0, bm1, inv, m0, m1);
+    const float mlo = (f & 2) ? m1 : m0, mhi = (f & 2) ? m0 : m1;
+    uint32_t w0 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((0 ^ f) << 4)), mlo);
+    uint32_t w1 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((1 ^ f) << 4)), mlo);
+    uint32_t w2 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((2 ^ f) << 4)), mhi);
+    uint32_t w3 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((3 ^ f) << 4)), mhi);
+    perm4(w0, w1, w2, w3, f);
+    put_q(p, make_uint4(w0, w1, w2, w3));
+    put_s(p, sf2);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// encode: x [rows][6144] BF16 -> values / scales / row scales
+// ---------------------------------------------------------------------------------------------
+template <bool STATIC>
+__global__ void __launch_bounds__(kOpsWarps * 32, 1)
+encode_rows_kernel(const char* __restrict__ x, int rows, char* values, long vpitch, char* scales, long spitch,
+                   float* row_scales, float inv_static, uint32_t* err) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  WarpSmem ws = carve(smem, warp);
+  if (lane == 0) { mbar_init(ws.bar, 1); mbar_init(ws.bar + 1, 1); }
+  mbar_init_fence();
+  __syncwarp();
+  const int stride = gridDim.x * kOpsWarps;
+  int row = blockIdx.x * kOpsWarps + warp;
+  uint8_t* buf[2] = {ws.a, ws.b};
+  if (lane == 0 && row < rows) { mbar_arrive_expect(ws.bar, kRowB); bulk_load(buf[0], x + (size_t)row * kRowB, kRowB, ws.bar); }
+  for (int it = 0; row < rows; row += stride, it++) {
+    const int nxt = row + stride;
+    if (lane == 0 && nxt < rows) {
+      mbar_arrive_expect(ws.bar + ((it + 1) & 1), kRowB);
+      bulk_load(buf[(it + 1) & 1], x + (size_t)nxt * kRowB, kRowB, ws.bar + ((it + 1) & 1));
+    }
+    wait_row(ws.bar + (it & 1), (uint32_t)((it >> 1) & 1), err);
+    char* vrow = values + (size_t)row * vpitch;
+    char* srow = scales + (size_t)row * spitch;
+    float rs;
+    encode_row_from_smem(buf[it & 1], lane, inv_static, STATIC, rs,
+                         [&](int p, uint4 q) { *reinterpret_cast<uint4*>(vrow + 16 * p) = q; },
+                         [&](int p, uint32_t sf2) { *reinterpret_cast<uint16_t*>(srow + 2 * p) = (uint16_t)sf2; });
+    if (!STATIC && lane == 0) row_scales[row] = rs;
+    __syncwarp();   // every lane is done with buf[it & 1] before it is refilled two iterations later
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode-sum: NS sources -> BF16 row; optional re-encode of the FP32 sum (two-shot owner step)
+// ---------------------------------------------------------------------------------------------
+struct SrcList {
+  const char* base[kMaxRanksOps];
+  const float* rs[kMaxRanksOps];
+  float gs[kMaxRanksOps];
+};
+
+template <int NS, bool REENC>
+__global__ void __launch_bounds__(kOpsWarps * 32, 1)
+decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int f = (lane >> 1) & 3;
+  WarpSmem ws = carve(smem, warp);
+  const int stride = gridDim.x * kOpsWarps;
+  bool pending_store = false;
+  for (int row = blockIdx.x * kOpsWarps + warp; row < rows; row += stride) {
+    float rsv[NS];
+#pragma unroll
+    for (int s = 0; s < NS; s++) rsv[s] = src.rs[s] ? src.rs[s][row] : src.gs[s];
+    auto sum_pair = [&](int p, float* acc) {
+      zero32(acc);
+#pragma unroll
+      for (int s = 0; s < NS; s++) {
+        const char* r = src.base[s] + (size_t)row * pitch;
+        uint4 q = __ldcg(reinterpret_cast<const uint4*>(r + 16 * p));
+        const uint32_t sf2 = __ldcg(reinterpret_cast<const unsigned short*>(r + kValueBytes + 2 * p));
+        perm4(q.x, q.y, q.z, q.w, f);
+        const F2 e = e4m3_unpack2(sf2);
+        const float s0 = __fmul_rn(e.lo, rsv[s]), s1 = __fmul_rn(e.hi, rsv[s]);
+        const F2 sa = f2_splat((f & 2) ? s1 : s0), sb = f2_splat((f & 2) ? s0 : s1);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          F2 v[4];
+          e2m1_unpack8(w[k], v);
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            F2 a; a.lo = acc[8 * k + 2 * i]; a.hi = acc[8 * k + 2 * i + 1];
+            a = f2_fma(v[i], k < 2 ? sa : sb, a);
+            acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
+          }
+        }
+      }
+    };
+    if (lane == 0 && pending_store) bulk_wait_source_free<0>();
+    __syncwarp();
+    RowScale sc2;
+    if (REENC) {
+      float am = 0.0f;
+#pragma unroll 1
+      for (int j = 0; j < 6; j++) { float acc[32]; sum_pair(lane + 32 * j, acc); am = absmax32(acc, am); }
+      sc2 = row_scale_from_amax(warp_max(am));
+    }
+#pragma unroll 1
+    for (int j = 0; j < 6; j++) {
+      const int p = lane + 32 * j;
+      float acc[32];
+      sum_pair(p, acc);
+      if (REENC) {
+        uint4 q;
+        uint32_t sf2 = encode_pair_f32<true>(acc, sc2.inv, q);   // slot order in, slot order out
+        // decode of the re-encoding, still in slot order
+        zero32(acc);
+        {
+          const F2 e = e4m3_unpack2(sf2);
+          const F2 sa = f2_splat(__fmul_rn(e.lo, sc2.rs)), sb = f2_splat(__fmul_rn(e.hi, sc2.rs));
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            F2 v[4];
+            e2m1_unpack8(w[k], v);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              F2 a; a.lo = 0.0f; a.hi = 0.0f;
+              a = f2_fma(v[i], k < 2 ? sa : sb, a);
+              acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
+            }
+          }
+        }
+        perm4(q.x, q.y, q.z, q.w, f);
+        if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
+        char* r = rec_out + (size_t)row * kRecStride;
+        *reinterpret_cast<uint4*>(r + 16 * p) = q;
+        *reinterpret_cast<uint16_t*>(r + kValueBytes + 2 * p) = (uint16_t)sf2;
+      }
+      uint4 o[4];
+      pack32_bf16(acc, o);
+#pragma unroll
+      for (int k = 0; k < 4; k++) sts16(ws.o + p * 64 + ((k ^ f) << 4), o[k]);
+    }
+    if (REENC && lane == 0) {
+      const uint32_t b = __float_as_uint(sc2.rs);
+      *reinterpret_cast<uint4*>(rec_out + (size_t)row * kRecStride + kQRowBytes) = make_uint4(b, b, b, b);
+    }
+    fence_smem_to_async();
+    __syncwarp();
+    if (lane == 0) { bulk_store(out + (size_t)row * kRowB, ws.o, kRowB); bulk_commit(); }
+    pending_store = true;
+  }
+  if (lane == 0) bulk_wait_done<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
+// add + Gemma RMSNorm:  z = x + res, res_out = bf16(z), y = (bf16(z) * rinv) * (wbias + w)
+// ---------------------------------------------------------------------------------------------
+template <int EPI>
+__global__ void __launch_bounds__(kOpsWarps * 32, 1)
+add_rmsnorm_kernel(const char* __restrict__ x, const char* __restrict__ res_in, char* res_out,
+                   const char* __restrict__ weight, float eps, float wbias, float qscale, char* out, char* outq,
+                   int rows, uint32_t* err) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int f = (lane >> 1) & 3;
+  WarpSmem ws = carve(smem, warp);
+  if (lane == 0) { mbar_init(ws.bar, 1); }
+  mbar_init_fence();
+  __syncwarp();
+  const int stride = gridDim.x * kOpsWarps;
+  int it = 0;
+  for (int row = blockIdx.x * kOpsWarps + warp; row < rows; row += stride, it++) {
+    if (lane == 0) {
+      bulk_wait_source_free<0>();     // the previous row's stores have left the buffers
+      mbar_arrive_expect(ws.bar, 2 * kRowB);
+      bulk_load(ws.a, x + (size_t)row * kRowB, kRowB, ws.bar);
+      bulk_load(ws.b, res_in + (size_t)row * kRowB, kRowB, ws.bar);
+    }
+    wait_row(ws.bar, (uint32_t)(it & 1), err);
+    uint4 zb[6][4];
+    float g6[6];
+#pragma unroll
+    for (int j = 0; j < 6; j++) {
+      const int p = lane + 32 * j;
+      float acc[32];
+      uint4 r[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const uint4 c = lds16(ws.a + p * 64 + ((k ^ f) << 4));
+        const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const F2 t = bf16x2_to_f2(cw[i]); acc[8 * k + 2 * i] = t.lo; acc[8 * k + 2 * i + 1] = t.hi; }
+        r[k] = lds16(ws.b + p * 64 + ((k ^ f) << 4));
+      }
+      const float sp = add_residual_sumsq(acc, r);
+      pack32_bf16(acc, zb[j]);
+#pragma unroll
+      for (int k = 0; k < 4; k++) sts16(ws.b + p * 64 + ((k ^ f) << 4), zb[j][k]);
+      g6[j] = warp_sum_butterfly(sp);
+    }
+    fence_smem_to_async();
+    __syncwarp();
+    if (lane == 0) bulk_store(res_out + (size_t)row * kRowB, ws.b, kRowB);
+    float ss = g6[0];
+#pragma unroll
+    for (int g = 1; g < 6; g++) ss = __fadd_rn(ss, g6[g]);
+    const float rinv = norm_rinv(ss, eps);
+#pragma unroll
+    for (int j = 0; j < 6; j++) {
+      const int p = lane + 32 * j;
+      uint4 wt[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) wt[k] = __ldg(reinterpret_cast<const uint4*>(weight + p * 64 + ((k ^ f) << 4)));
+      float y[32];
+      norm_pair(zb[j], wt, rinv, wbias, y);
+      uint4 yb[4];
+      pack32_bf16(y, yb);
+      if (EPI == 1) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) sts16(ws.o + p * 64 + ((k ^ f) << 4), yb[k]);
+      } else if (EPI == 2) {
+        uint4 q;
+        uint32_t sf2 = quant_pair_nvfp4_out(yb, qscale, q);
+        perm4(q.x, q.y, q.z, q.w, f);
+        if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
+        sts16(ws.o + p * 16, q);
+        *reinterpret_cast<uint16_t*>(ws.o + kValueBytes + 2 * p) = (uint16_t)sf2;
+      } else {
+        uint4 v[2];
+        const uint32_t e = quant_pair_mxfp8_out(yb, v);
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(v);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+          *reinterpret_cast<uint2*>(ws.o + p * 32 + ((k ^ f) << 3)) = make_uint2(vw[2 * k], vw[2 * k + 1]);
+        ws.o[kHidden + p] = (uint8_t)e;
+      }
+    }
+    fence_smem_to_async();
+    __syncwarp();
+    if (lane == 0) {
+      if (EPI == 1) bulk_store(out + (size_t)row * kRowB, ws.o, kRowB);
+      else if (EPI == 2) bulk_store(outq + (size_t)row * kQRowBytes, ws.o, kQRowBytes);
+      else bulk_store(outq + (size_t)row * kMxRowBytes, ws.o, kMxRowBytes);
+      bulk_commit();
+    }
+  }
+  if (lane == 0) bulk_wait_done<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
+// sentinel fill of a window made of `nbuf` buffers of `buf_bytes` (slots of kRecStride from each buffer start)
+// ---------------------------------------------------------------------------------------------
+__global__ void fill_sentinel_kernel(uint4* win, size_t buf_units, int nbuf) {
+  const size_t total = buf_units * nbuf;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t u = (i % buf_units) % (kRecStride / 16);
+    uint4 v;
+    if (u < kValueBytes / 16) v = make_uint4(kSentWord, kSentWord, kSentWord, kSentWord);
+    else if (u < kQRowBytes / 16) v = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+    else if (u == kQRowBytes / 16) v = make_uint4(kSentRow, kSentRow, kSentRow, kSentRow);
+    else v = make_uint4(0, 0, 0, 0);
+    win[i] = v;
+  }
+}
+
+// A word the kernels above set when a local row load did not arrive in time.
+static uint32_t* ops_error_word() {
+  static thread_local uint32_t* p[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!p[dev]) {
+    if (cudaMalloc(&p[dev], 16) != cudaSuccess) return nullptr;
+    cudaMemset(p[dev], 0, 16);
+  }
+  return p[dev];
+}
+
+static int ops_grid(int rows) {
+  const int sms = device_sm_count();
+  const int need = (rows + kOpsWarps - 1) / kOpsWarps;
+  return need < sms ? (need > 0 ? need : 1) : sms;
+}
+
+template <class K>
+static bool ensure_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+}  // namespace fp4ar
+
+using namespace fp4ar;
+
+extern "C" int fp4ar_encode(const void* x, int rows, void* values, long vpitch, void* scales, long spitch,
+                            float* row_scales, fp4ar_stream stream) {
+  if (!x || !values || !scales || !row_scales || rows < 0 || vpitch < kValueBytes || spitch < kScaleBytes) return FP4AR_ERR_ARGUMENT;
+  if (((uintptr_t)x | (uintptr_t)values | (uintptr_t)vpitch) & 15) return FP4AR_ERR_ARGUMENT;
+  if (((uintptr_t)scales | (uintptr_t)spitch) & 1) return FP4AR_ERR_ARGUMENT;
+  if (rows == 0) return FP4AR_OK;
+  uint32_t* err = ops_error_word();
+  if (!err || !ensure_smem(encode_rows_kernel<false>, kOpsSmem)) return cuda_fail();
+  encode_rows_kernel<false><<<ops_grid(rows), kOpsWarps * 32, kOpsSmem, (cudaStream_t)stream>>>(
+      (const char*)x, rows, (char*)values, vpitch, (char*)scales, spitch, row_scales, 0.0f, err);
+  return cuda_check_launch();
+}
+
+extern "C" int fp4ar_encode_static(const void* x, int rows, float gs, void* qrows, fp4ar_stream stream) {
+  if (!x || !qrows || rows < 0 || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
+  if (((uintptr_t)x | (uintptr_t)qrows) & 15) return FP4AR_ERR_ARGUMENT;
+  if (rows == 0) return FP4AR_OK;
+  uint32_t* err = ops_error_word();
+  if (!err || !ensure_smem(encode_rows_kernel<true>, kOpsSmem)) return cuda_fail();
+  encode_rows_kernel<true><<<ops_grid(rows), kOpsWarps * 32, kOpsSmem, (cudaStream_t)stream>>>(
+      (const char*)x, rows, (char*)qrows, kQRowBytes, (char*)qrows + kValueBytes, kQRowBytes, nullptr, 1.0f / gs, err);
+  return cuda_check_launch();
+}
+
+template <bool REENC>
+static int launch_decode(int nsrc, const void* const* src, long pitch, const float* const* rs, const float* gs, int rows,
+                         void* rec_out, void* out, cudaStream_t st) {
+  if (nsrc < 1 || nsrc > FP4AR_MAX_RANKS || !src || !out || rows < 0 || pitch < kQRowBytes || (pitch & 15)) return FP4AR_ERR_ARGUMENT;
+  if (REENC && !rec_out) return FP4AR_ERR_ARGUMENT;
+  SrcList sl;
+  for (int s = 0; s < kMaxRanksOps; s++) { sl.base[s] = nullptr; sl.rs[s] = nullptr; sl.gs[s] = 0.0f; }
+  for (int s = 0; s < nsrc; s++) {
+    if (!src[s] || ((uintptr_t)src[s] & 15)) return FP4AR_ERR_ARGUMENT;
+    sl.base[s] = (const char*)src[s];
+    sl.rs[s] = rs ? rs[s] : nullptr;
+    if (!sl.rs[s]) { if (!gs) return FP4AR_ERR_ARGUMENT; sl.gs[s] = gs[s]; }
+  }
+  if (rows == 0) return FP4AR_OK;
+  const int grid = ops_grid(rows), blk = kOpsWarps * 32;
+#define FP4AR_DEC_CASE(N)                                                                                   \
+  case N:                                                                                                   \
+    if (!ensure_smem(decode_sum_kernel<N, REENC>, kOpsSmem)) return cuda_fail();                             \
+    decode_sum_kernel<N, REENC><<<grid, blk, kOpsSmem, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);  \
+    break;
+  switch (nsrc) {
+    FP4AR_DEC_CASE(1) FP4AR_DEC_CASE(2) FP4AR_DEC_CASE(3) FP4AR_DEC_CASE(4)
+    FP4AR_DEC_CASE(5) FP4AR_DEC_CASE(6) FP4AR_DEC_CASE(7) FP4AR_DEC_CASE(8)
+  }
+#undef FP4AR_DEC_CASE
+  return cuda_check_launch();
+}
+
+extern "C" int fp4ar_decode_sum(int nsrc, const void* const* src, long pitch, const float* const* rs, const float* gs,
+                                int rows, void* out, fp4ar_stream stream) {
+  return launch_decode<false>(nsrc, src, pitch, rs, gs, rows, nullptr, out, (cudaStream_t)stream);
+}
+extern "C" int fp4ar_reduce_reencode(int nsrc, const void* const* src, long pitch, const float* const* rs,
+                                     const float* gs, int rows, void* rec_out, void* out, fp4ar_stream stream) {
+  return launch_decode<true>(nsrc, src, pitch, rs, gs, rows, rec_out, out, (cudaStream_t)stream);
+}
+
+extern "C" int fp4ar_add_rmsnorm(const void* x, const void* res_in, void* res_out, const void* weight, float eps,
+                                 float wbias, int epilogue, float qscale, void* out, void* outq, int rows,
+                                 fp4ar_stream stream) {
+  if (!x || !res_in || !res_out || !weight || rows < 0) return FP4AR_ERR_ARGUMENT;
+  if (epilogue < 1 || epilogue > 3) return FP4AR_ERR_ARGUMENT;
+  if (epilogue == 1 ? !out : !outq) return FP4AR_ERR_ARGUMENT;
+  if (((uintptr_t)x | (uintptr_t)res_in | (uintptr_t)res_out | (uintptr_t)weight | (uintptr_t)out | (uintptr_t)outq) & 15)
+    return FP4AR_ERR_ARGUMENT;
+  if (rows == 0) return FP4AR_OK;
+  uint32_t* err = ops_error_word();
+  if (!err) return cuda_fail();
+  const int grid = ops_grid(rows), blk = kOpsWarps * 32;
+  cudaStream_t st = (cudaStream_t)stream;
+#define FP4AR_NORM_CASE(E)                                                                                         \
+  case E:                                                                                                          \
+    if (!ensure_smem(add_rmsnorm_kernel<E>, kOpsSmem)) return cuda_fail();                                          \
+    add_rmsnorm_kernel<E><<<grid, blk, kOpsSmem, st>>>((const char*)x, (const char*)res_in, (char*)res_out,        \
+                                                       (const char*)weight, eps, wbias, qscale, (char*)out,        \
+                                                       (char*)outq, rows, err);                                    \
+    break;
+  switch (epilogue) { FP4AR_NORM_CASE(1) FP4AR_NORM_CASE(2) FP4AR_NORM_CASE(3) }
+#undef FP4AR_NORM_CASE
+  return cuda_check_launch();
+}
+
+extern "C" int fp4ar_fill_sentinel(void* window, size_t buffer_bytes, int nbuffers, fp4ar_stream stream) {
+  if (!window || ((uintptr_t)window & 15) || (buffer_bytes & 15) || nbuffers < 1) return FP4AR_ERR_ARGUMENT;
+  fill_sentinel_kernel<<<1024, 256, 0, (cudaStream_t)stream>>>((uint4*)window, buffer_bytes / 16, nbuffers);
+  return cuda_check_launch();
+}

@@ -1,0 +1,180 @@
+"""A slow, independent model of the row codec in numpy + exact rational arithmetic.
+
+It shares no code with csrc/oracle/oracle.cpp: conversions are nearest-neighbour searches over the
+value tables with ties to the even code, and every fused multiply-add is evaluated exactly with
+`fractions.Fraction` and rounded once.  The CPU test-suite uses it to pin the C++ model, which in turn
+pins the GPU kernels.
+"""
+from fractions import Fraction
+
+import numpy as np
+
+H = 6144
+E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float64)
+
+
+def e4m3_values():
+    v = np.zeros(127, np.float64)
+    for b in range(127):
+        e, m = b >> 3, b & 7
+        v[b] = (1 + m / 8) * 2.0 ** (e - 7) if e else (m / 8) * 2.0 ** -6
+    return v
+
+
+E4M3 = e4m3_values()
+
+
+def bf16_to_f32(bits):
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x):
+    u = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r[nan] = 0x7FFF
+    return r
+
+
+def e2m1_encode(x):
+    """Nearest grid point, ties to the even code, saturating; NaN -> 7."""
+    x = np.asarray(x, np.float32)
+    out = np.zeros(x.shape, np.uint8)
+    flat, o = x.reshape(-1), out.reshape(-1)
+    for i, v in enumerate(flat):
+        if np.isnan(v):
+            o[i] = 7
+            continue
+        a = abs(float(v))
+        best = 0
+        if a >= 6.0:      # saturate (also keeps the distance comparison below exact for huge inputs)
+            o[i] = 7 | (8 if np.signbit(v) else 0)
+            continue
+        for c in range(1, 8):
+            d0, d1 = abs(a - E2M1[best]), abs(a - E2M1[c])
+            if d1 < d0 or (d1 == d0 and c % 2 == 0):
+                best = c
+        o[i] = best | (8 if np.signbit(v) else 0)
+    return out
+
+
+def e4m3_encode(x):
+    """Non-negative input. Nearest of the 127 finite values, ties to the even byte, saturating; NaN -> 0x7F."""
+    x = np.asarray(x, np.float32)
+    out = np.zeros(x.shape, np.uint8)
+    flat, o = x.reshape(-1), out.reshape(-1)
+    for i, v in enumerate(flat):
+        if np.isnan(v):
+            o[i] = 0x7F
+            continue
+        a = float(v)
+        if a >= 448:
+            o[i] = 0x7E
+            continue
+        j = int(np.searchsorted(E4M3, a))
+        cands = [c for c in (j - 1, j) if 0 <= c < 127]
+        best = cands[0]
+        for c in cands[1:]:
+            d0, d1 = abs(a - E4M3[best]), abs(a - E4M3[c])
+            if d1 < d0 or (d1 == d0 and c % 2 == 0):
+                best = c
+        o[i] = best
+    return out
+
+
+def round_f32(fr: Fraction) -> np.float32:
+    """Round an exact rational to float32, nearest even (normal and subnormal results)."""
+    if fr == 0:
+        return np.float32(0.0)
+    sign = -1 if fr < 0 else 1
+    a = abs(fr)
+    # exponent e with 2^e <= a < 2^(e+1)
+    e = a.numerator.bit_length() - a.denominator.bit_length()
+    if Fraction(2) ** e > a:
+        e -= 1
+    elif Fraction(2) ** (e + 1) <= a:
+        e += 1
+    e = max(e, -126)
+    scaled = a / (Fraction(2) ** (e - 23))          # 24-bit significand target
+    q, r = divmod(scaled.numerator, scaled.denominator)
+    twice = 2 * r
+    if twice > scaled.denominator or (twice == scaled.denominator and (q & 1)):
+        q += 1
+    val = float(q) * 2.0 ** (e - 23)
+    if val > 3.4028234663852886e38:
+        val = float("inf")
+    return np.float32(sign * val)
+
+
+def fma_f32(a, b, c) -> np.float32:
+    for v in (a, b, c):
+        if not np.isfinite(v):
+            return np.float32(np.float32(a) * np.float32(b) + np.float32(c))
+    r = Fraction(float(a)) * Fraction(float(b)) + Fraction(float(c))
+    if r == 0:
+        # IEEE sign of an exact zero sum: +0 unless both addends are -0
+        prod_neg = np.signbit(np.float32(a)) != np.signbit(np.float32(b))
+        return np.float32(-0.0) if (prod_neg and np.signbit(np.float32(c))) else np.float32(0.0)
+    return round_f32(r)
+
+
+def encode_row(f, inv=None, canon=True):
+    """f: 6144 float32.  Returns (values u8[3072], scales u8[384], rs float32)."""
+    f = np.asarray(f, np.float32)
+    am = np.float32(np.max(np.abs(f[~np.isnan(f)]))) if np.any(~np.isnan(f)) else np.float32(0)
+    with np.errstate(all="ignore"):
+        rs = np.float32(am / np.float32(2688))
+        if inv is None:
+            inv = np.float32(2688) / am if am > 0 else np.float32(0)
+        inv = np.float32(inv)
+        v = np.zeros(3072, np.uint8)
+        s = np.zeros(384, np.uint8)
+        for b in range(384):
+            blk = f[16 * b:16 * b + 16]
+            bm = np.float32(np.max(np.abs(blk)))
+            sv = np.float32(np.float32(bm * inv) / np.float32(6))
+            sb = int(e4m3_encode(np.array([sv]))[0])
+            s[b] = sb
+            sff = np.float32(E4M3[sb]) if sb < 127 else np.float32(np.nan)
+            m = np.float32(inv / sff) if sff > 0 else np.float32(0)
+            q = e2m1_encode((blk * m).astype(np.float32))
+            if canon:
+                q[q == 8] = 0
+            v[8 * b:8 * b + 8] = q[0::2] | (q[1::2] << 4)
+    return v, s, rs
+
+
+def decode_acc_row(acc, v, s, rs):
+    vals = np.concatenate([E2M1, -E2M1]).astype(np.float32)
+    out = np.array(acc, np.float32)
+    with np.errstate(all="ignore"):
+        for b in range(384):
+            sff = np.float32(E4M3[s[b]]) if s[b] < 127 else np.float32(np.nan)
+            S = np.float32(sff * np.float32(rs))
+            for i in range(16):
+                n = (int(v[(16 * b + i) >> 1]) >> (4 * (i & 1))) & 15
+                out[16 * b + i] = fma_f32(vals[n], S, out[16 * b + i])
+    return out
+
+
+def row_sumsq(z):
+    z = np.asarray(z, np.float32)
+    G = []
+    for j in range(6):
+        t = []
+        for l in range(32):
+            p = z[32 * (l + 32 * j):32 * (l + 32 * j) + 32]
+            e = o = np.float32(0)
+            for i in range(16):
+                e = fma_f32(p[2 * i], p[2 * i], e)
+                o = fma_f32(p[2 * i + 1], p[2 * i + 1], o)
+            t.append(np.float32(e + o))
+        d = 16
+        while d:
+            t = [np.float32(t[l] + t[l ^ d]) for l in range(32)]
+            d >>= 1
+        G.append(t[0])
+    ss = G[0]
+    for g in G[1:]:
+        ss = np.float32(ss + g)
+    return ss
