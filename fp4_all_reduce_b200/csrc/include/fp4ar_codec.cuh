@@ -99,12 +99,17 @@ __device__ __forceinline__ uint32_t e2m1_pack8(F2 a, F2 b, F2 c, F2 d) {
   return w;
 }
 
-// One word of E2M1 nibbles -> eight exact floats (as four pairs).
+// One word of E2M1 nibbles -> eight exact floats (as four pairs).  Each byte is narrowed from a
+// shifted 32-bit value: splitting the word with mov.b32 {lo,hi} / mov.b16 {b0,b1} is mis-assembled
+// for the upper half by ptxas 12.9 on sm_100a (elements 4 and 5 come out wrong), which the GPU
+// codec tests guard against.
 __device__ __forceinline__ void e2m1_unpack8(uint32_t w, F2* out) {
   uint32_t h0, h1, h2, h3;
-  asm("{ .reg .b8 q0, q1, q2, q3; .reg .b16 l, u;\n"
-      "  mov.b32 {l, u}, %4;\n"
-      "  mov.b16 {q0, q1}, l; mov.b16 {q2, q3}, u;\n"
+  asm("{ .reg .b8 q0, q1, q2, q3; .reg .b32 t1, t2, t3;\n"
+      "  cvt.u8.u32 q0, %4;\n"
+      "  shr.u32 t1, %4, 8;  cvt.u8.u32 q1, t1;\n"
+      "  shr.u32 t2, %4, 16; cvt.u8.u32 q2, t2;\n"
+      "  shr.u32 t3, %4, 24; cvt.u8.u32 q3, t3;\n"
       "  cvt.rn.f16x2.e2m1x2 %0, q0;\n"
       "  cvt.rn.f16x2.e2m1x2 %1, q1;\n"
       "  cvt.rn.f16x2.e2m1x2 %2, q2;\n"
@@ -286,19 +291,25 @@ __device__ __forceinline__ bool rowscale_pending(uint32_t bits) { return bits ==
 // Reference project: kernels/fused_norm/lnorm_epi.cuh:23-70; its approximate rsqrt is replaced by
 // exact operations so that the host model can reproduce the result.
 // ---------------------------------------------------------------------------------------------
-// z (in place in acc) and the pair's sum of squares: even and odd elements are accumulated
-// separately in element order, then added.
+// z (in place in acc) and the pair's sum of squares.  Per 8-value chunk the even and the odd elements
+// are accumulated separately in element order and added; the four chunk sums are combined as
+// (t0 + t1) + (t2 + t3), which is the same number for every order in which a lane may hold its chunks.
 __device__ __forceinline__ float add_residual_sumsq(float* acc, const uint4* res) {
   const uint32_t* rw = reinterpret_cast<const uint32_t*>(res);
-  F2 ss = f2_splat(0.0f);
+  float t[4];
 #pragma unroll
-  for (int i = 0; i < 16; i++) {
-    F2 a; a.lo = acc[2 * i]; a.hi = acc[2 * i + 1];
-    a = f2_add(a, bf16x2_to_f2(rw[i]));
-    ss = f2_fma(a, a, ss);
-    acc[2 * i] = a.lo; acc[2 * i + 1] = a.hi;
+  for (int c = 0; c < 4; c++) {
+    F2 ss = f2_splat(0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      F2 a; a.lo = acc[8 * c + 2 * i]; a.hi = acc[8 * c + 2 * i + 1];
+      a = f2_add(a, bf16x2_to_f2(rw[4 * c + i]));
+      ss = f2_fma(a, a, ss);
+      acc[8 * c + 2 * i] = a.lo; acc[8 * c + 2 * i + 1] = a.hi;
+    }
+    t[c] = __fadd_rn(ss.lo, ss.hi);
   }
-  return __fadd_rn(ss.lo, ss.hi);
+  return __fadd_rn(__fadd_rn(t[0], t[1]), __fadd_rn(t[2], t[3]));
 }
 __device__ __forceinline__ float warp_sum_butterfly(float v) {
 #pragma unroll

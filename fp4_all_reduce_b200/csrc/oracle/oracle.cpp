@@ -134,7 +134,10 @@ void decode_acc_row(float* acc, const uint8_t* v, const uint8_t* s, float rs) {
 }
 
 // Sum of squares of one row in the fixed order every kernel reproduces:
-//   pair p (32 values): e = fma over even elements in order, o = fma over odd elements, s_p = e + o
+//   chunk c of a pair (8 values): e = fma over its even elements in order, o = fma over its odd elements, t_c = e + o
+//   pair p (32 values = chunks 0..3): s_p = (t_0 + t_1) + (t_2 + t_3)
+//     (a tree that does not change when chunks 0<->1 / 2<->3 or the halves are swapped, which lets a
+//      kernel keep the chunks of a pair in any of its four lane-dependent orders)
 //   group j (pairs 32j..32j+31): butterfly over the 32 pair sums with partner distance 16,8,4,2,1
 //   row: ((((G0 + G1) + G2) + G3) + G4) + G5
 float row_sumsq(const float* z) {
@@ -143,9 +146,16 @@ float row_sumsq(const float* z) {
     float t[32];
     for (int l = 0; l < 32; l++) {
       const float* p = z + 32 * (l + 32 * j);
-      float e = 0.f, o = 0.f;
-      for (int i = 0; i < 16; i++) { e = std::fmaf(p[2 * i], p[2 * i], e); o = std::fmaf(p[2 * i + 1], p[2 * i + 1], o); }
-      t[l] = e + o;
+      float tc[4];
+      for (int c = 0; c < 4; c++) {
+        float e = 0.f, o = 0.f;
+        for (int i = 0; i < 4; i++) {
+          e = std::fmaf(p[8 * c + 2 * i], p[8 * c + 2 * i], e);
+          o = std::fmaf(p[8 * c + 2 * i + 1], p[8 * c + 2 * i + 1], o);
+        }
+        tc[c] = e + o;
+      }
+      t[l] = (tc[0] + tc[1]) + (tc[2] + tc[3]);
     }
     for (int d = 16; d; d >>= 1) {
       float u[32];

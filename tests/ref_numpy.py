@@ -164,11 +164,14 @@ def row_sumsq(z):
         t = []
         for l in range(32):
             p = z[32 * (l + 32 * j):32 * (l + 32 * j) + 32]
-            e = o = np.float32(0)
-            for i in range(16):
-                e = fma_f32(p[2 * i], p[2 * i], e)
-                o = fma_f32(p[2 * i + 1], p[2 * i + 1], o)
-            t.append(np.float32(e + o))
+            tc = []
+            for c in range(4):
+                e = o = np.float32(0)
+                for i in range(4):
+                    e = fma_f32(p[8 * c + 2 * i], p[8 * c + 2 * i], e)
+                    o = fma_f32(p[8 * c + 2 * i + 1], p[8 * c + 2 * i + 1], o)
+                tc.append(np.float32(e + o))
+            t.append(np.float32(np.float32(tc[0] + tc[1]) + np.float32(tc[2] + tc[3])))
         d = 16
         while d:
             t = [np.float32(t[l] + t[l ^ d]) for l in range(32)]

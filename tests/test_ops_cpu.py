@@ -1,0 +1,47 @@
+"""CPU tests of the op surface: schemas, fake (meta) implementations, argument validation, window sizes."""
+import ctypes as C
+
+import pytest
+import torch
+
+from fp4_all_reduce_b200 import _native as N
+from fp4_all_reduce_b200.ops import allreduce as A  # noqa: F401  (registers torch.ops.fp4ar)
+
+
+def test_fake_impls_give_shapes_without_a_gpu():
+    with torch._subclasses.FakeTensorMode():
+        x = torch.empty(37, 6144, dtype=torch.bfloat16)
+        res = torch.empty(37, 6144, dtype=torch.bfloat16)
+        w = torch.empty(6144, dtype=torch.bfloat16)
+        xq = torch.empty(37, 3456, dtype=torch.uint8)
+        assert torch.ops.fp4ar.all_reduce(x, 1).shape == (37, 6144)
+        assert torch.ops.fp4ar.all_reduce_nvfp4(xq, [1.0, 2.0], 1).dtype == torch.bfloat16
+        assert torch.ops.fp4ar.all_reduce_add_rms_norm(x, res, w, 1e-6, 1.0, 1).shape == (37, 6144)
+        assert torch.ops.fp4ar.all_reduce_add_rms_norm_nvfp4(xq, [1.0, 2.0], res, w, 1e-6, 1.0, 1).shape == (37, 6144)
+        assert torch.ops.fp4ar.all_reduce_add_rms_norm_quant(x, res, w, 1e-6, 1.0, 2, 1.0, 1).shape == (37, 3456)
+        assert torch.ops.fp4ar.all_reduce_add_rms_norm_quant(x, res, w, 1e-6, 1.0, 3, 1.0, 1).shape == (37, 6336)
+        q, rs = torch.ops.fp4ar.encode(x)
+        assert q.shape == (37, 3456) and rs.shape == (37,)
+        assert torch.ops.fp4ar.decode_sum([q, q], [rs, rs]).shape == (37, 6144)
+
+
+def test_unknown_context_id_is_an_error():
+    with pytest.raises(RuntimeError):
+        A._ctx(987654)
+
+
+def test_window_bytes_and_argument_validation_without_a_gpu():
+    lib = N.cuda()
+    assert lib.fp4ar_window_bytes(16384, 6144, 2) == 2 * 2 * 16384 * 3584   # 2 buffers x 2 sources x rows x slot
+    assert lib.fp4ar_window_bytes(16384, 6144, 8) % (2 << 20) == 0
+    assert lib.fp4ar_window_bytes(16384, 4096, 2) == 0      # only hidden 6144
+    assert lib.fp4ar_window_bytes(16384, 6144, 3) == 0      # 1, 2, 4, 8 ranks
+    assert lib.fp4ar_window_bytes(0, 6144, 2) == 0
+    # a window that is too small or a null pointer is rejected before any CUDA call
+    ctx = C.c_void_p()
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    assert lib.fp4ar_create(C.byref(ctx), 0, 2, 0, 1024, 6144, ptrs, 4096) == 1
+    ptrs = (C.c_void_p * 2)(None, None)
+    assert lib.fp4ar_create(C.byref(ctx), 0, 2, 0, 1024, 6144, ptrs, 1 << 30) == 1
+    assert lib.fp4ar_launch(None, None, None) == 1
+    assert b"sm_100a" in lib.fp4ar_build_info()
