@@ -107,7 +107,7 @@ def reduce_reencode(qrows: Sequence[torch.Tensor], row_scales=None, gs=None) -> 
 
 def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
                 weight_bias: float = 1.0, epilogue: int = N.EPI_NORM_BF16, qscale: float = 1.0,
-                inplace_residual: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+                inplace_residual: bool = False, out: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """z = x + residual; residual' = bf16(z); y = (bf16(z) * rinv) * (weight_bias + weight).
     Returns (y as BF16 [rows,6144] | NVFP4 rows [rows,3456] | MXFP8 rows [rows,6336], residual')."""
     _req(x, torch.bfloat16, N.HIDDEN, "x")
@@ -116,13 +116,13 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
         raise ValueError("weight must be a CUDA BF16 tensor of 6144 elements")
     rows = x.shape[0]
     res_out = residual if inplace_residual else torch.empty_like(residual)
-    out = outq = None
+    given, out, outq = out, None, None
     if epilogue == N.EPI_NORM_BF16:
-        out = torch.empty_like(x)
+        out = given if given is not None else torch.empty_like(x)
     elif epilogue == N.EPI_NORM_NVFP4:
-        outq = torch.empty(rows, N.QROW_BYTES, dtype=torch.uint8, device=x.device)
+        outq = given if given is not None else torch.empty(rows, N.QROW_BYTES, dtype=torch.uint8, device=x.device)
     elif epilogue == N.EPI_NORM_MXFP8:
-        outq = torch.empty(rows, N.MXROW_BYTES, dtype=torch.uint8, device=x.device)
+        outq = given if given is not None else torch.empty(rows, N.MXROW_BYTES, dtype=torch.uint8, device=x.device)
     else:
         raise ValueError("epilogue must be 1 (BF16), 2 (NVFP4) or 3 (MXFP8)")
     with torch.cuda.device(x.device):

@@ -141,9 +141,12 @@ class Fp4ArContext(_Base):
     def __init__(self, max_rows: int, group=None, device: Optional[torch.device] = None):
         import torch.distributed as dist
 
-        self.group = group if group is not None else dist.group.WORLD
-        self.rank = dist.get_rank(self.group)
-        self.nranks = dist.get_world_size(self.group)
+        if dist.is_available() and dist.is_initialized():
+            self.group = group if group is not None else dist.group.WORLD
+            self.rank = dist.get_rank(self.group)
+            self.nranks = dist.get_world_size(self.group)
+        else:                      # no process group: a one-rank context (encode, decode of the own encoding, epilogue)
+            self.group, self.rank, self.nranks = None, 0, 1
         self.max_rows = max_rows
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         lib = N.cuda()

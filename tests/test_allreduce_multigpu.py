@@ -1,0 +1,44 @@
+"""The five-phase gate and its negative controls on real GPUs (one process per GPU over NVLink).
+Skipped on machines with fewer than two GPUs; the single-GPU form is tests/test_allreduce_emulated_gpu.py."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc, extra, port):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "fp4_all_reduce_b200.harness.gate_dist"] + extra
+    p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    recs = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{") and '"kind": "check"' in l]
+    return p.returncode, recs, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def _world_sizes():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [w for w in (2, 4, 8) if w <= n]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gate_passes(world):
+    if world not in _world_sizes():
+        pytest.skip(f"needs {world} GPUs")
+    rc, recs, log = _run(world, ["--rows", "1024,333", "--inputs", "bf16,nvfp4", "--epilogues", "0,1", "--reps", "20",
+                                 "--graph-calls", "5", "--graph-reps", "5", "--skew-reps", "4"], 29611 + world)
+    assert rc == 0, log
+    assert len(recs) == 8 and all(r["pass"] for r in recs), recs
+
+
+@pytest.mark.parametrize("negctl", ["stale", "flip"])
+def test_negative_controls_fail_every_cell(negctl):
+    rc, recs, log = _run(2, ["--rows", "512", "--reps", "6", "--graph-calls", "3", "--graph-reps", "2", "--skew-reps", "2",
+                             "--negctl", negctl], 29631)
+    assert rc == 3, log
+    assert recs and all(not r["pass"] for r in recs), recs
