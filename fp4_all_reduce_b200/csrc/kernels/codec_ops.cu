@@ -460,3 +460,61 @@ extern "C" int fp4ar_fill_sentinel(void* window, size_t buffer_bytes, int nbuffe
   fill_sentinel_kernel<<<1024, 256, 0, (cudaStream_t)stream>>>((uint4*)window, buffer_bytes / 16, nbuffers);
   return cuda_check_launch();
 }
+
+// ---------------------------------------------------------------------------------------------
+// fp4ar_reduce_reencode_noalloc (declared and documented in include/fp4ar_noalloc.h): the owner step with
+// its record buffer in a fixed device array instead of caller memory.  No counterpart in the reference.
+// ---------------------------------------------------------------------------------------------
+#include "../include/fp4ar_noalloc.h"
+#include <cstdio>
+#include <mutex>
+
+// The records of one call: FP4AR_NOALLOC_MAX_ROWS slots of kRecStride bytes.  In host code this name is only a
+// handle for cudaGetSymbolAddress; the kernel receives the device address looked up below.
+static __device__ __align__(256) unsigned char g_noalloc_records[(size_t)FP4AR_NOALLOC_MAX_ROWS * fp4ar::kRecStride];
+
+static thread_local char g_noalloc_error[256] = "";
+
+static int noalloc_fail(int code, const char* text) {
+  std::snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", text);
+  return code;
+}
+
+// Device address of the array on the current device; looked up once per device, with that device current.
+static void* noalloc_records_on_current_device() {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_records);
+    if (e != cudaSuccess || !p) {
+      fp4ar::set_last_cuda_error(e, "cudaGetSymbolAddress(g_noalloc_records)");
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  return addr[dev];
+}
+
+extern "C" const char* fp4ar_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int fp4ar_reduce_reencode_noalloc(int nsrc, const void* const* src, long pitch, const float* const* rs,
+                                             const float* gs, int rows, void* out_bf16, fp4ar_stream stream) {
+  g_noalloc_error[0] = 0;
+  if (rows > FP4AR_NOALLOC_MAX_ROWS) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg), "fp4ar_reduce_reencode_noalloc: %d rows exceed the built-in record array of %d rows",
+                  rows, FP4AR_NOALLOC_MAX_ROWS);
+    return noalloc_fail(FP4AR_ERR_ARGUMENT, msg);
+  }
+  void* records = noalloc_records_on_current_device();
+  if (!records)
+    return noalloc_fail(FP4AR_ERR_CUDA, "fp4ar_reduce_reencode_noalloc: the record array's device address is unavailable");
+  const int rc = launch_decode<true>(nsrc, src, pitch, rs, gs, rows, records, out_bf16, (cudaStream_t)stream);
+  if (rc == FP4AR_ERR_ARGUMENT) return noalloc_fail(rc, "fp4ar_reduce_reencode_noalloc: bad source list, pitch or output pointer");
+  if (rc != FP4AR_OK) return noalloc_fail(rc, "fp4ar_reduce_reencode_noalloc: the launch failed (see fp4ar_last_cuda_error)");
+  return FP4AR_OK;
+}
