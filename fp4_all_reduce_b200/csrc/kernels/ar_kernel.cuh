@@ -71,7 +71,9 @@ struct ArShape {
   static constexpr int NSG = IN == 2 ? P : P - 1;                    // sources read from the window
   // Two-shot owners hold a whole FP32 row slice in registers and the norm epilogue holds BF16 z:
   // those shapes get fewer, fatter threads.
-  static constexpr int kMaxTeams = (ALGO == 1 || EPI > 0) ? 6 : 8;
+  // (Register budget per thread = 65536 / (32 * T * kMaxTeams).)
+  static constexpr int kHeavy = (ALGO == 1 || EPI > 0) ? 1 : 0;
+  static constexpr int kMaxTeams = T == 2 ? (kHeavy ? 6 : 8) : (T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : 3));
   static __host__ __device__ constexpr int smem_bytes(int teams) { return teams * kTeamBytes + kCtaExtra; }
 };
 

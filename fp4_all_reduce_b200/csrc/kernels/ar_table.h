@@ -11,14 +11,14 @@ struct ArKernelEntry {
   int team_bytes, cta_extra, max_teams;
 };
 
-constexpr int kTeamWarps = 2;   // warps per row team in every compiled shape
+constexpr int kDefaultTeamWarps = 3;   // warps per row team unless a launch asks for another compiled width
 
-template <int P, int ALGO, int IN, int EPI>
+template <int P, int ALGO, int IN, int EPI, int T>
 inline ArKernelEntry make_entry() {
-  using S = ArShape<P, ALGO, IN, EPI, kTeamWarps>;
+  using S = ArShape<P, ALGO, IN, EPI, T>;
   ArKernelEntry e;
-  e.P = P; e.algo = ALGO; e.input = IN; e.epi = EPI; e.T = kTeamWarps;
-  e.fn = reinterpret_cast<const void*>(&ar_kernel<P, ALGO, IN, EPI, kTeamWarps>);
+  e.P = P; e.algo = ALGO; e.input = IN; e.epi = EPI; e.T = T;
+  e.fn = reinterpret_cast<const void*>(&ar_kernel<P, ALGO, IN, EPI, T>);
   e.team_bytes = S::kTeamBytes; e.cta_extra = S::kCtaExtra; e.max_teams = S::kMaxTeams;
   return e;
 }

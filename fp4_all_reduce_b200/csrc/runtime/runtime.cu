@@ -7,6 +7,7 @@
 // slots of 3584 B, shared by every algorithm and input kind (the reference keeps 3 buffers for each of
 // one-shot, two-shot and NVFP4-input regions).
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -59,7 +60,7 @@ static std::vector<ArKernelEntry>& kernel_table() {
   static std::vector<ArKernelEntry> table;
   static std::once_flag once;
   std::call_once(once, [] {
-    ArKernelEntry buf[128];
+    ArKernelEntry buf[256];
     int n = 0;
     ar_register_p1(buf, &n); ar_register_p2(buf, &n); ar_register_p2b(buf, &n);
     ar_register_p4(buf, &n); ar_register_p4b(buf, &n); ar_register_p8(buf, &n); ar_register_p8b(buf, &n);
@@ -68,10 +69,20 @@ static std::vector<ArKernelEntry>& kernel_table() {
   });
   return table;
 }
-static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi) {
+static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi, int T) {
   for (const ArKernelEntry& e : kernel_table())
-    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi) return &e;
+    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi && e.T == T) return &e;
   return nullptr;
+}
+// Team width: tune[2] of the call if set, else FP4AR_TEAM_WARPS from the environment, else the default.
+static int team_warps_for(const fp4ar_args& a) {
+  if (a.tune[2] > 0) return a.tune[2];
+  static const int from_env = [] {
+    const char* s = std::getenv("FP4AR_TEAM_WARPS");
+    const int v = s ? std::atoi(s) : 0;
+    return v > 0 ? v : kDefaultTeamWarps;
+  }();
+  return from_env;
 }
 
 struct Geometry {
@@ -223,7 +234,7 @@ extern "C" const char* fp4ar_build_info(void) {
   if (s.empty()) {
     char b[256];
     std::snprintf(b, sizeof(b), "fp4ar sm_100a cuda-runtime %d shapes %d team-warps %d", CUDART_VERSION,
-                  (int)kernel_table().size(), kTeamWarps);
+                  (int)kernel_table().size(), kDefaultTeamWarps);
     s = b;
   }
   return s.c_str();
@@ -241,7 +252,7 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (algo == FP4AR_ALGO_AUTO) algo = c->nranks <= 2 ? FP4AR_ALGO_ONESHOT : FP4AR_ALGO_TWOSHOT;
   if (algo != FP4AR_ALGO_ONESHOT && algo != FP4AR_ALGO_TWOSHOT) return FP4AR_ERR_ARGUMENT;
   if (c->nranks == 1) algo = FP4AR_ALGO_ONESHOT;
-  const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue);
+  const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, team_warps_for(a0));
   if (!ke) return FP4AR_ERR_UNSUPPORTED;
 
   ArParams prm;
