@@ -87,7 +87,11 @@ def oracle() -> C.CDLL:
 
 
 def cuda_library_path() -> Path:
-    return _LIB / "libfp4ar.so"
+    """In-tree library, or the file named by FP4AR_LIBRARY (for tuning builds with extra counters)."""
+    import os
+
+    override = os.environ.get("FP4AR_LIBRARY")
+    return Path(override) if override else _LIB / "libfp4ar.so"
 
 
 @functools.lru_cache(maxsize=None)

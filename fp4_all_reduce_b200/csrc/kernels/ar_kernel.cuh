@@ -55,6 +55,7 @@ struct ArParams {
   int rows, ctas_per_rank, flags;
   int cap, capo;
   unsigned long long buf_bytes, timeout_ns;
+  unsigned long long* phase_cycles;   // tuning builds only (-DFP4AR_PHASE_TIMERS): 16 per-phase cycle counters
 };
 
 template <int P, int ALGO, int IN, int EPI, int T>
@@ -107,6 +108,20 @@ __device__ __forceinline__ void decode_acc_lane(float* acc, uint4 q, uint32_t sf
   const float s0 = __fmul_rn(e.lo, rs), s1 = __fmul_rn(e.hi, rs);
   decode_acc_slots(acc, q.x, q.y, q.z, q.w, (f & 2) ? s1 : s0, (f & 2) ? s0 : s1);
 }
+
+// Per-phase cycle counters for tuning builds (-DFP4AR_PHASE_TIMERS); absent from the production library.
+#ifdef FP4AR_PHASE_TIMERS
+#define FP4AR_PHASE(idx)                                                               \
+  do {                                                                                 \
+    if (leader && team == 0) {                                                         \
+      const long long now_ = clock64();                                                \
+      atomicAdd(&prm.phase_cycles[idx], (unsigned long long)(now_ - phase_t0_));         \
+      phase_t0_ = now_;                                                                \
+    }                                                                                  \
+  } while (0)
+#else
+#define FP4AR_PHASE(idx) do { } while (0)
+#endif
 
 template <int T>
 struct TeamSync {
@@ -351,9 +366,18 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   // =============================================================================================
   // main pipeline
   // =============================================================================================
+#ifdef FP4AR_PHASE_TIMERS
+  long long phase_t0_ = clock64();
+#endif
   for (int k = 0; k <= nk; k++) {
+    FP4AR_PHASE(0);
+#ifdef FP4AR_EXPERIMENT_WAIT1
+    if (leader) bulk_wait_source_free<1>();
+#else
     if (leader) bulk_wait_source_free<0>();
+#endif
     tsync.sync();
+    FP4AR_PHASE(1);   // drain wait + barrier
     if (leader && k < nk) {
       if (IN == 0 && EPI > 0 && k + 1 < nk) {
         const int b = (k + 1) % 3;
@@ -372,6 +396,158 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
       }
     }
 
+    // ------------------------------------------------------------------ early window loads of row k-1
+    // One-shot rows and rows this rank owns: every source pushed its record during the previous step, so the
+    // loads are issued now and their latency overlaps what follows; stage B validates them and falls back to
+    // polling for whatever had not arrived.  Rows owned by a peer: that peer re-encodes the row during this very
+    // step (before it encodes its own row k), so their loads are issued after stage A.
+    constexpr int kPfSrc = NSG > 0 ? NSG : 1;
+    constexpr bool kPfAll = NJ * NSG <= 8;            // a whole row of every window source fits in registers
+    constexpr int kPfData = kPfAll ? kPfSrc : 1;
+    constexpr bool kTwoShot = ALGO == 1 && P > 1;
+    const char* psrc[kPfSrc];
+    uint32_t prs[kPfSrc];
+    uint4 pq[NJ][kPfData];
+    uint32_t psf[NJ][kPfData];
+    bool row1_owned = false, row1_has_rs = false;
+    float row1_rs2 = 0.0f;                            // row scale of the re-encoding of an owned row
+    if (k >= 1) {
+      const int row1 = row_of(k - 1);
+      if constexpr (!kTwoShot) {
+#pragma unroll
+        for (int i = 0; i < NSG; i++) psrc[i] = my_buf + os_slot(window_source(i), row1);
+        row1_has_rs = IN == 0;
+      } else {
+        row1_owned = (row1 % P) == me;
+        if (row1_owned) {
+#pragma unroll
+          for (int i = 0; i < NSG; i++) psrc[i] = my_buf + rs_slot(window_source(i), row1);
+          row1_has_rs = IN == 0;
+        } else {
+          psrc[0] = my_buf + ag_slot(row1 % P, row1);
+          row1_has_rs = !(loopb && IN >= 1);
+        }
+      }
+      if (!kTwoShot || row1_owned) {
+#pragma unroll
+        for (int i = 0; i < NSG; i++)
+          if (row1_has_rs) prs[i] = poll_ld4(psrc[i] + kQRowBytes);
+        if (kPfAll) {
+#pragma unroll
+          for (int jj = 0; jj < NJ; jj++) {
+            const int p = lane + 32 * (tw + T * jj);
+#pragma unroll
+            for (int i = 0; i < NSG; i++) {
+              pq[jj][i] = poll_ld16(psrc[i] + 16 * p);
+              psf[jj][i] = poll_ld2(psrc[i] + kValueBytes + 2 * p);
+            }
+          }
+        }
+      }
+    }
+    auto settle_rs = [&](uint32_t bits, const char* rec, int row, int src, int phase) -> float {
+      return rowscale_pending(bits) ? poll_rowscale(rec, row, src, phase) : __uint_as_float(bits);
+    };
+
+    FP4AR_PHASE(2);   // early loads issued
+    // ------------------------------------------------------------------ owner step of row k-1 (two-shot)
+    // Reduce every source, re-encode, broadcast.  It runs before this rank encodes row k so that the peers,
+    // which encode their row k meanwhile, find the broadcast when they turn to row k-1.
+    if constexpr (kTwoShot) {
+      if (k >= 1 && row1_owned) {
+        const int row = row_of(k - 1);
+        uint8_t* rec_own = recs + ((k - 1) % NREC) * kRecStride;
+        float wrs[kPfSrc];
+#pragma unroll
+        for (int i = 0; i < NSG; i++) {
+          const int s = window_source(i);
+          wrs[i] = IN == 0 ? settle_rs(prs[i], psrc[i], row, s, 2) : prm.gs[s];
+        }
+        float own_rs = 0.0f;
+        if (IN == 0) own_rs = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
+        if (IN == 1) own_rs = prm.gs[me];
+        float sums[NJ][32];
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+          const int p = lane + 32 * (tw + T * j);
+          uint4 wq[kPfSrc];
+          uint32_t wsf[kPfSrc];
+#pragma unroll
+          for (int i = 0; i < NSG; i++) {
+            if (kPfAll) { wq[i] = pq[j][i]; wsf[i] = psf[j][i]; }
+            else { wq[i] = poll_ld16(psrc[i] + 16 * p); wsf[i] = poll_ld2(psrc[i] + kValueBytes + 2 * p); }
+          }
+#pragma unroll
+          for (int i = 0; i < NSG; i++)
+            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(psrc[i], p, wq[i], wsf[i], row, window_source(i), 2);
+          zero32(sums[j]);
+          if (!xport) {
+#pragma unroll
+            for (int i = 0; i <= NSG; i++) {
+              if (IN != 2 && i == me) {
+                const uint4 q = lds16(rec_own + 16 * p);
+                const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
+                decode_acc_lane(sums[j], q, sf2, own_rs, f);
+              }
+              if (i < NSG) decode_acc_lane(sums[j], wq[i], wsf[i], wrs[i], f);
+            }
+            am = absmax32(sums[j], am);
+          }
+        }
+        am = warp_max(am);
+        {
+          float mine[NJ], g6[6];
+#pragma unroll
+          for (int j = 0; j < NJ; j++) mine[j] = am;
+          team_gather6(mine, g6);   // also orders every lane's reads of rec_own before the rewrite below
+#pragma unroll
+          for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
+        }
+        const RowScale sc = row_scale_from_amax(am);
+        row1_rs2 = sc.rs;
+        if (!xport) {
+#pragma unroll
+          for (int j = 0; j < NJ; j++) {
+            const int p = lane + 32 * (tw + T * j);
+            uint4 q;
+            uint32_t sf2 = encode_pair_f32<true>(sums[j], sc.inv, q);   // slot order
+            lane_permute4(q.x, q.y, q.z, q.w, f);
+            if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
+            sts16(rec_own + 16 * p, q);
+            *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)sf2;
+          }
+          if (leader) {
+            const uint32_t rb4 = __float_as_uint(sc.rs);
+            sts16(rec_own + kQRowBytes, make_uint4(rb4, rb4, rb4, rb4));
+          }
+        } else if (IN == 2) {
+#pragma unroll
+          for (int j = 0; j < NJ; j++) {
+            const int p = lane + 32 * (tw + T * j);
+            sts16(rec_own + 16 * p, make_uint4(0x11111111u, 0x11111111u, 0x11111111u, 0x11111111u));
+            *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)0x3838u;
+          }
+          if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
+        } else if (IN == 1) {
+          if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
+        }
+        fence_smem_to_async();
+        tsync.sync();
+        if (leader) {
+#pragma unroll
+          for (int d = 0; d < P; d++) {
+            if (d == me) continue;
+            char* dst = (loopb ? my_buf : io.win[d] + buf_off) + ag_slot(me, row);
+            bulk_store(dst, rec_own, kRecPayload);
+          }
+#pragma unroll
+          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(psrc[i]), sentinel, kRecPayload);
+        }
+      }
+    }
+
+    FP4AR_PHASE(3);   // owner step
     // ------------------------------------------------------------------ stage A: row k
     if (k < nk) {
       const int row = row_of(k);
@@ -380,6 +556,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
         const int b = k % NXB1;
         const uint8_t* xrow = xb + b * kRowBytes;
         mbar_wait_bounded(xbar + b, (uint32_t)((k / NXB1) & 1), wctx, row);
+        FP4AR_PHASE(4);   // wait for x
         if (!xport) {
           uint32_t bmp[NJ];
           float am = 0.0f;
@@ -406,6 +583,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
             for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
           }
           const RowScale sc = row_scale_from_amax(am);
+          FP4AR_PHASE(5);   // amax pass + exchange
 #pragma unroll
           for (int j = 0; j < NJ; j++) {
             const int p = lane + 32 * (tw + T * j);
@@ -478,50 +656,37 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
       }
     }
 
-    // ------------------------------------------------------------------ stage B: row k-1
+    FP4AR_PHASE(6);   // encode pass 2 + push
+    // ------------------------------------------------------------------ stage B: finish row k-1
     if (k >= 1) {
       const int k1 = k - 1;
       const int row = row_of(k1);
       uint8_t* rec_own = recs + (k1 % NREC) * kRecStride;
       const int owner = row % P;
 
-      if constexpr (ALGO == 0 || P == 1) {
+      if constexpr (!kTwoShot) {
         // ---- one-shot: every rank decodes every source in rank order ----
-        const char* wsrc[NSG > 0 ? NSG : 1];
-        float wrs[NSG > 0 ? NSG : 1];
+        float wrs[kPfSrc];
 #pragma unroll
         for (int i = 0; i < NSG; i++) {
           const int s = window_source(i);
-          wsrc[i] = my_buf + os_slot(s, row);
-          wrs[i] = IN == 0 ? poll_rowscale(wsrc[i], row, s, 1) : prm.gs[s];
+          wrs[i] = IN == 0 ? settle_rs(prs[i], psrc[i], row, s, 1) : prm.gs[s];
         }
         float own_rs = 0.0f;
         if (IN == 0) own_rs = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
         if (IN == 1) own_rs = prm.gs[me];
-        constexpr int JB = (NJ * NSG <= 6) ? NJ : 1;   // pairs whose window loads are issued together
-        uint4 wq[JB][NSG > 0 ? NSG : 1];
-        uint32_t wsf[JB][NSG > 0 ? NSG : 1];
         auto fill = [&](int j, float* acc) {
-          if (j % JB == 0) {
-#pragma unroll
-            for (int jj = 0; jj < JB; jj++) {
-              const int p = lane + 32 * (tw + T * (j + jj));
-#pragma unroll
-              for (int i = 0; i < NSG; i++) {
-                wq[jj][i] = poll_ld16(wsrc[i] + 16 * p);
-                wsf[jj][i] = poll_ld2(wsrc[i] + kValueBytes + 2 * p);
-              }
-            }
-#pragma unroll
-            for (int jj = 0; jj < JB; jj++) {
-              const int p = lane + 32 * (tw + T * (j + jj));
-#pragma unroll
-              for (int i = 0; i < NSG; i++)
-                if (values_pending(wq[jj][i]) | scales_pending(wsf[jj][i]))
-                  poll_pair(wsrc[i], p, wq[jj][i], wsf[jj][i], row, window_source(i), 1);
-            }
-          }
           const int p = lane + 32 * (tw + T * j);
+          uint4 wq[kPfSrc];
+          uint32_t wsf[kPfSrc];
+#pragma unroll
+          for (int i = 0; i < NSG; i++) {
+            if (kPfAll) { wq[i] = pq[j][i]; wsf[i] = psf[j][i]; }
+            else { wq[i] = poll_ld16(psrc[i] + 16 * p); wsf[i] = poll_ld2(psrc[i] + kValueBytes + 2 * p); }
+          }
+#pragma unroll
+          for (int i = 0; i < NSG; i++)
+            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(psrc[i], p, wq[i], wsf[i], row, window_source(i), 1);
           zero32(acc);
           if (!xport) {
 #pragma unroll
@@ -531,145 +696,55 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
                 const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
                 decode_acc_lane(acc, q, sf2, own_rs, f);
               }
-              if (i < NSG) decode_acc_lane(acc, wq[j % JB][i], wsf[j % JB][i], wrs[i], f);
+              if (i < NSG) decode_acc_lane(acc, wq[i], wsf[i], wrs[i], f);
             }
           }
         };
         auto extra = [&]() {
 #pragma unroll
-          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(wsrc[i]), sentinel, kRecPayload);
+          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(psrc[i]), sentinel, kRecPayload);
         };
         finish_row(k1, row, fill, extra);
       } else {
       if (owner == me) {
-        // ---- two-shot, owned row: reduce all sources, re-encode, broadcast, output the decode of the re-encoding ----
-        const char* wsrc[NSG];
-        float wrs[NSG];
-#pragma unroll
-        for (int i = 0; i < NSG; i++) {
-          const int s = window_source(i);
-          wsrc[i] = my_buf + rs_slot(s, row);
-          wrs[i] = IN == 0 ? poll_rowscale(wsrc[i], row, s, 2) : prm.gs[s];
-        }
-        float own_rs = 0.0f;
-        if (IN == 0) own_rs = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
-        if (IN == 1) own_rs = prm.gs[me];
-        float sums[NJ][32];
-        float am = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-          const int p = lane + 32 * (tw + T * j);
-          uint4 wq[NSG];
-          uint32_t wsf[NSG];
-#pragma unroll
-          for (int i = 0; i < NSG; i++) {
-            wq[i] = poll_ld16(wsrc[i] + 16 * p);
-            wsf[i] = poll_ld2(wsrc[i] + kValueBytes + 2 * p);
-          }
-#pragma unroll
-          for (int i = 0; i < NSG; i++)
-            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(wsrc[i], p, wq[i], wsf[i], row, window_source(i), 2);
-          zero32(sums[j]);
-          if (!xport) {
-#pragma unroll
-            for (int i = 0; i <= NSG; i++) {
-              if (IN != 2 && i == me) {
-                const uint4 q = lds16(rec_own + 16 * p);
-                const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
-                decode_acc_lane(sums[j], q, sf2, own_rs, f);
-              }
-              if (i < NSG) decode_acc_lane(sums[j], wq[i], wsf[i], wrs[i], f);
-            }
-            am = absmax32(sums[j], am);
-          }
-        }
-        am = warp_max(am);
-        {
-          float mine[NJ], g6[6];
-#pragma unroll
-          for (int j = 0; j < NJ; j++) mine[j] = am;
-          team_gather6(mine, g6);   // also orders every lane's reads of rec_own before the rewrite below
-#pragma unroll
-          for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
-        }
-        const RowScale sc = row_scale_from_amax(am);
-        if (!xport) {
-#pragma unroll
-          for (int j = 0; j < NJ; j++) {
-            const int p = lane + 32 * (tw + T * j);
-            uint4 q;
-            uint32_t sf2 = encode_pair_f32<true>(sums[j], sc.inv, q);   // slot order
-            lane_permute4(q.x, q.y, q.z, q.w, f);
-            if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
-            sts16(rec_own + 16 * p, q);
-            *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)sf2;
-          }
-          if (leader) {
-            const uint32_t rb4 = __float_as_uint(sc.rs);
-            sts16(rec_own + kQRowBytes, make_uint4(rb4, rb4, rb4, rb4));
-          }
-        } else if (IN == 2) {
-#pragma unroll
-          for (int j = 0; j < NJ; j++) {
-            const int p = lane + 32 * (tw + T * j);
-            sts16(rec_own + 16 * p, make_uint4(0x11111111u, 0x11111111u, 0x11111111u, 0x11111111u));
-            *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)0x3838u;
-          }
-          if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
-        } else if (IN == 1) {
-          if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
-        }
-        fence_smem_to_async();
-        tsync.sync();
-        if (leader) {
-#pragma unroll
-          for (int d = 0; d < P; d++) {
-            if (d == me) continue;
-            char* dst = (loopb ? my_buf : io.win[d] + buf_off) + ag_slot(me, row);
-            bulk_store(dst, rec_own, kRecPayload);
-          }
-#pragma unroll
-          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(wsrc[i]), sentinel, kRecPayload);
-        }
+        // ---- two-shot, owned row: its re-encoding sits in rec_own; every rank outputs the decode of that ----
         auto fill = [&](int j, float* acc) {
           const int p = lane + 32 * (tw + T * j);
           zero32(acc);
           if (!xport) {
             const uint4 q = lds16(rec_own + 16 * p);
             const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
-            decode_acc_lane(acc, q, sf2, sc.rs, f);
+            decode_acc_lane(acc, q, sf2, row1_rs2, f);
           }
         };
         auto extra = [&]() {};
         finish_row(k1, row, fill, extra);
       } else {
         // ---- two-shot, row owned by a peer: wait for its broadcast and decode that single record ----
-        const char* src = my_buf + ag_slot(owner, row);
-        const float rs = (loopb && IN >= 1) ? prm.gs[me] : poll_rowscale(src, row, owner, 3);
-        uint4 wq[NJ];
-        uint32_t wsf[NJ];
+        const char* src = psrc[0];
+        uint32_t rsb = 0;
+        if (row1_has_rs) rsb = poll_ld4(src + kQRowBytes);
+#pragma unroll
+        for (int jj = 0; jj < NJ; jj++) {
+          const int p = lane + 32 * (tw + T * jj);
+          pq[jj][0] = poll_ld16(src + 16 * p);
+          psf[jj][0] = poll_ld2(src + kValueBytes + 2 * p);
+        }
+        const float rs = row1_has_rs ? settle_rs(rsb, src, row, owner, 3) : prm.gs[me];
         auto fill = [&](int j, float* acc) {
-          if (j == 0) {
-#pragma unroll
-            for (int jj = 0; jj < NJ; jj++) {
-              const int p = lane + 32 * (tw + T * jj);
-              wq[jj] = poll_ld16(src + 16 * p);
-              wsf[jj] = poll_ld2(src + kValueBytes + 2 * p);
-            }
-#pragma unroll
-            for (int jj = 0; jj < NJ; jj++) {
-              const int p = lane + 32 * (tw + T * jj);
-              if (values_pending(wq[jj]) | scales_pending(wsf[jj])) poll_pair(src, p, wq[jj], wsf[jj], row, owner, 3);
-            }
-          }
+          const int p = lane + 32 * (tw + T * j);
+          uint4 wq = pq[j][0];
+          uint32_t wsf = psf[j][0];
+          if (values_pending(wq) | scales_pending(wsf)) poll_pair(src, p, wq, wsf, row, owner, 3);
           zero32(acc);
-          if (!xport) decode_acc_lane(acc, wq[j], wsf[j], rs, f);
+          if (!xport) decode_acc_lane(acc, wq, wsf, rs, f);
         };
         auto extra = [&]() { bulk_store(const_cast<char*>(src), sentinel, kRecPayload); };
         finish_row(k1, row, fill, extra);
       }
       }
     }
+    FP4AR_PHASE(7);   // finish
     if (leader) bulk_commit();
   }
 

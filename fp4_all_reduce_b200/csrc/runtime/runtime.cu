@@ -85,6 +85,12 @@ static int team_warps_for(const fp4ar_args& a) {
   return from_env;
 }
 
+#ifdef FP4AR_PHASE_TIMERS
+}  // namespace fp4ar
+static unsigned long long* phase_buffer();
+namespace fp4ar {
+#endif
+
 struct Geometry {
   int cap, capo;
   size_t buf_bytes, total;
@@ -289,6 +295,9 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   prm.flags = (a0.mode == FP4AR_MODE_XPORT ? kFlagXport : 0) | (a0.mode == FP4AR_MODE_COMPUTE ? kFlagLoopback : 0);
   prm.cap = c->geo.cap; prm.capo = c->geo.capo;
   prm.buf_bytes = c->geo.buf_bytes; prm.timeout_ns = c->timeout_ns;
+#ifdef FP4AR_PHASE_TIMERS
+  prm.phase_cycles = phase_buffer();
+#endif
 
   // host-side bounds check of the largest window offset this call can touch
   {
@@ -326,3 +335,17 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   FP4AR_CUDA(cudaLaunchKernelExC(&cfg, ke->fn, kargs));
   return FP4AR_OK;
 }
+
+#ifdef FP4AR_PHASE_TIMERS
+// Tuning builds only: per-phase cycle counters filled by the kernel (see FP4AR_PHASE in ar_kernel.cuh).
+static unsigned long long* g_phase_dev = nullptr;
+static unsigned long long* phase_buffer() {
+  if (!g_phase_dev) { cudaMalloc(&g_phase_dev, 16 * sizeof(unsigned long long)); cudaMemset(g_phase_dev, 0, 16 * sizeof(unsigned long long)); }
+  return g_phase_dev;
+}
+extern "C" int fp4ar_debug_phase_cycles(unsigned long long* out16) {
+  if (cudaMemcpy(out16, phase_buffer(), 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) return FP4AR_ERR_CUDA;
+  cudaMemset(phase_buffer(), 0, 16 * sizeof(unsigned long long));
+  return FP4AR_OK;
+}
+#endif

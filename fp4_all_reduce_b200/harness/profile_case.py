@@ -21,6 +21,22 @@ from ..utils import data as D
 from ..ops import codec
 
 
+class _SoloRank(Fp4ArContext):
+    """Rank 0 of an nranks group with every window on this GPU; only usable in compute (loop-back) mode."""
+
+    def __init__(self, nranks, rows, dev):
+        import ctypes as C
+        self.group, self.rank, self.nranks, self.max_rows, self.device = None, 0, nranks, rows, dev
+        lib = N.cuda()
+        self.window_bytes = int(lib.fp4ar_window_bytes(rows, N.HIDDEN, nranks))
+        self.window = torch.empty(self.window_bytes, dtype=torch.uint8, device=dev)
+        self._handle = None
+        ptrs = (C.c_void_p * nranks)(*([self.window.data_ptr()] * nranks))
+        ctx = C.c_void_p()
+        N.check(lib.fp4ar_create(C.byref(ctx), 0, nranks, dev.index or 0, rows, N.HIDDEN, ptrs, self.window_bytes), "fp4ar_create")
+        self._ctx = ctx
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ranks", type=int, default=1)
@@ -32,6 +48,8 @@ def main(argv=None) -> int:
     ap.add_argument("--calls", type=int, default=3)
     ap.add_argument("--teams", type=int, default=0)
     ap.add_argument("--team-warps", type=int, default=0)
+    ap.add_argument("--solo", action="store_true",
+                    help="create rank 0 of a --ranks group on this GPU and launch it alone (needs --mode 2: every push is looped back)")
     ns = ap.parse_args(argv)
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
@@ -55,7 +73,12 @@ def main(argv=None) -> int:
                          res_out=res[r] if ns.epilogue else None, weight=w if ns.epilogue else None, outq=outq[r],
                          qscale=168.0, teams=ns.teams, team_warps=ns.team_warps)
 
-    if P == 1:
+    if ns.solo:
+        if ns.mode != N.MODE_COMPUTE:
+            raise SystemExit("--solo needs --mode 2 (a rank launched alone would wait for peers that never run)")
+        ctx = _SoloRank(P, rows, dev)
+        launch = lambda: ctx.launch(args(0))
+    elif P == 1:
         ctx = Fp4ArContext(rows, device=dev)
         launch = lambda: ctx.launch(args(0))
     else:
