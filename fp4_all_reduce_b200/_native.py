@@ -73,6 +73,7 @@ def oracle() -> C.CDLL:
     lib.fp4ar_oracle_encode.argtypes = [vp, C.c_int, vp, C.c_long, vp, C.c_long, vp, C.c_int]
     lib.fp4ar_oracle_encode_f32.argtypes = [vp, C.c_int, vp, C.c_long, vp, C.c_long, vp, C.c_int]
     lib.fp4ar_oracle_encode_static.argtypes = [vp, C.c_int, C.c_float, vp, C.c_long, vp, C.c_long]
+    lib.fp4ar_oracle_encode_static_f32.argtypes = [vp, C.c_int, C.c_int, C.c_float, vp, C.c_long, vp, C.c_long]
     lib.fp4ar_oracle_decode_acc.argtypes = [vp, C.c_int, vp, C.c_long, vp, C.c_long, vp, C.c_float]
     lib.fp4ar_oracle_f32_to_bf16.argtypes = [vp, vp, C.c_long]
     lib.fp4ar_oracle_canon_neg0.argtypes = [vp, vp, C.c_long]
@@ -120,6 +121,10 @@ def cuda() -> C.CDLL:
     lib.fp4ar_reduce_reencode.argtypes = [C.c_int, vpp, C.c_long, vpp, C.POINTER(C.c_float), C.c_int, vp, vp, vp]
     lib.fp4ar_add_rmsnorm.argtypes = [vp, vp, vp, vp, C.c_float, C.c_float, C.c_int, C.c_float, vp, vp, C.c_int, vp]
     lib.fp4ar_fill_sentinel.argtypes = [vp, C.c_size_t, C.c_int, vp]
+    lib.fp4ar_gemm_nvfp4.argtypes = [C.POINTER(PushView), C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp, vp, vp]
+    lib.fp4ar_gemm_nvfp4.restype = C.c_int
+    lib.fp4ar_gemm_status.argtypes = [C.POINTER(StatusWords)]
+    lib.fp4ar_gemm_status.restype = C.c_int
     for name in ("fp4ar_create", "fp4ar_create_emulated", "fp4ar_launch", "fp4ar_status", "fp4ar_set_timeout_ms",
                  "fp4ar_reset", "fp4ar_destroy", "fp4ar_get_push_view", "fp4ar_ctas_per_rank", "fp4ar_encode",
                  "fp4ar_encode_static", "fp4ar_decode_sum", "fp4ar_reduce_reencode", "fp4ar_add_rmsnorm",

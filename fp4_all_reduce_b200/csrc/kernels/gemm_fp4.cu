@@ -1,0 +1,368 @@
+// Row-parallel GEMM with an NVFP4 epilogue that pushes straight into the AllReduce receive windows.
+//
+//   partial[M, N] = X[M, K] (BF16, K contiguous) x Wt[N, K]^T (BF16, K contiguous), FP32 accumulate
+//   epilogue: every 16 consecutive outputs of a row are quantised with the static per-rank scale gs
+//             (block scale e4m3(rn(rn(blockmax/gs')/6)), values e2m1, -0 canonicalised: the static-scale row
+//             format of the AllReduce), and the row pieces are stored
+//               - into every rank's receive window (one-shot), or into the row owner's window (two-shot),
+//                 where the AllReduce kernel in "pushed input" mode finds them, and/or
+//               - into a local [M, N/2 + N/16] NVFP4 tensor.
+//
+// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.
+//   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
+//                              128-byte swizzle, completion on mbarriers
+//   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
+//                              shared-memory descriptors into TMEM; tcgen05.commit releases ring stages and
+//                              publishes finished accumulators; owns tcgen05.alloc / dealloc (512 columns =
+//                              two accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 2-5: epilogue      - tcgen05.ld (32 lanes x 32 columns per instruction), quantise, stage the row
+//                              pieces in shared memory, bulk-store them to the (peer) windows
+// Every wait is bounded; a wait that gives up raises a CTA-wide abort flag, the roles drain, TMEM is freed and
+// the status word reports it.
+//
+// The reference project has no such producer: its NVFP4-input kernels assume one and the harness emulates it
+// with a copy (README.md:76, docs/INTEGRATION.md:67-74, harness/fp4ar_bench.cu:205-215).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstring>
+#include <mutex>
+#include "../include/fp4ar.h"
+#include "../include/fp4ar_codec.cuh"
+#include "../include/fp4ar_async.cuh"
+#include "../include/fp4ar_gemm.h"
+#include "host_util.h"
+
+namespace fp4ar {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;            // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
+constexpr int kPieceBytes = kBN / 2 + kBN / 16;   // 144 B of one row of one tile: 128 value bytes + 16 scale bytes
+constexpr int kEpiBytes = kBM * kPieceBytes;      // 18 KB staging
+constexpr int kGemmThreads = 192;
+constexpr int kGemmSmem = kStages * kStageBytes + kEpiBytes + 256 + 1024;   // + barriers + alignment slack
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+  int M, N, K;
+  float inv_gs;
+  // push destination (nranks == 0: none)
+  char* win[kMaxRanksOps];
+  const uint32_t* call_counter;
+  unsigned long long buf_bytes;
+  int cap, capo, nranks, rank, two_shot;
+  // local outputs (optional)
+  char* local_q;       // [M][N/2 + N/16]
+  float* dbg_acc;      // [M][N]
+  StatusWords* status;
+  unsigned long long timeout_ns;
+};
+
+// ---- tcgen05 / TMA wrappers ----
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(holder)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{ .reg .pred p;\n"
+               "  setp.ne.b32 p, %4, 0;\n"
+               "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 BF16) with the 128-byte
+// swizzle: 8-row groups 1024 bytes apart, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile) {
+  uint64_t d = (uint64_t)((smem_addr(smem_tile) >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused with a swizzle), in 16-byte units
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // version
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D = F32, A = B = BF16, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+struct GemmWait {
+  volatile uint32_t* abort_flag;
+  StatusWords* status;
+  unsigned long long limit_ns;
+};
+// Bounded mbarrier wait; false when it gave up or the CTA is aborting.
+__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, const GemmWait& w, uint32_t what) {
+  if (mbar_test(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t n = 0;
+  while (!mbar_test(bar, parity)) {
+    if ((++n & 255u) == 0u) {
+      if (*w.abort_flag) return false;
+      if (global_timer_ns() - t0 > w.limit_ns) {
+        *w.abort_flag = 1u;
+        if (atomicCAS(&w.status->code, 0u, (uint32_t)kStatusLoadTimeout) == 0u) { w.status->detail = 16u + what; w.status->cta = blockIdx.x; }
+        atomicAdd(&w.status->count, 1u);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* ring = smem;
+  uint8_t* epi = smem + kStages * kStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi + kEpiBytes);   // [kStages]
+  uint64_t* empty = full + kStages;                                 // [kStages]
+  uint64_t* acc_full = empty + kStages;                             // [2]
+  uint64_t* acc_empty = acc_full + 2;                               // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = p.N / kBN, m_tiles = (p.M + kBM - 1) / kBM;
+  const int tiles = n_tiles * m_tiles, kblocks = p.K / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 128); }
+    *abort_flag = 0u;
+    mbar_init_fence();
+  }
+  if (warp == 1) { tmem_alloc(tmem_holder, kTmemCols); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  GemmWait gw{abort_flag, p.status, p.timeout_ns};
+
+  pdl_wait_prior_grids();   // the windows and the call counter belong to the previous kernel until here
+  pdl_release_dependents();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * kBN;
+        for (int kb = 0; kb < kblocks; kb++, it++) {
+          const int s = it % kStages;
+          if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
+            // giving up: let the loads already issued land before the CTA (and its shared memory) goes away
+            for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; back++) {
+              const uint32_t j = it - back;
+              uint32_t spins = 0;
+              while (!mbar_test(full + (j % kStages), (j / kStages) & 1u) && ++spins < (1u << 20)) {}
+            }
+            goto done;
+          }
+          mbar_arrive_expect(full + s, kStageBytes);
+          tma_load_2d(ring + s * kStageBytes, &map_a, kb * kBK, m0, full + s);
+          tma_load_2d(ring + s * kStageBytes + kABytes, &map_b, kb * kBK, n0, full + s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_i = 0;
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
+        const uint32_t a = tile_i & 1u;
+        if (!gemm_wait(acc_empty + a, ((tile_i >> 1) & 1u) ^ 1u, gw, 2)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * kBN;
+        for (int kb = 0; kb < kblocks; kb++, it++) {
+          const int s = it % kStages;
+          if (!gemm_wait(full + s, (it / kStages) & 1u, gw, 3)) goto done;
+          tc_fence_after();
+          const uint64_t da = umma_desc_k128(ring + s * kStageBytes);
+          const uint64_t db = umma_desc_k128(ring + s * kStageBytes + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; k++)
+            umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty + s);          // the stage is free once these MMAs have read it
+        }
+        umma_commit(acc_full + a);         // the accumulator is complete once everything above has run
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 = 128 threads = 128 rows)
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int r_in_tile = q * 32 + lane;
+    uint8_t* my_piece = epi + r_in_tile * kPieceBytes;
+    const size_t buf_off = p.nranks ? (size_t)(*p.call_counter & 1u) * p.buf_bytes : 0;
+    const int qrow_bytes = p.N / 2 + p.N / 16;
+    uint32_t tile_i = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
+      const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * kBN;
+      const uint32_t a = tile_i & 1u;
+      const int row = m0 + r_in_tile;
+      // warp-uniform verdict: the tcgen05.ld below is a warp-wide instruction
+      if (!__all_sync(0xffffffffu, gemm_wait(acc_full + a, (tile_i >> 1) & 1u, gw, 4))) break;
+      tc_fence_after();
+      bulk_wait_source_free<0>();   // this thread's previous pieces have left its staging row
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; c++) {
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * kBN + c * 32, v);
+        if (p.dbg_acc && row < p.M) {
+          float4* dst = reinterpret_cast<float4*>(p.dbg_acc + (size_t)row * p.N + n0 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+        uint4 qv;
+        const uint32_t sf2 = encode_pair_f32<true>(v, p.inv_gs, qv);
+        *reinterpret_cast<uint4*>(my_piece + 16 * c) = qv;
+        *reinterpret_cast<uint16_t*>(my_piece + kBN / 2 + 2 * c) = (uint16_t)sf2;
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty + a);                 // 128 arrivals hand the accumulator back to the MMA warp
+      fence_smem_to_async();
+      if (row < p.M) {
+        const size_t voff = (size_t)(n0 / 2), soff = (size_t)(p.N / 2 + n0 / 16);
+        if (p.local_q) {
+          char* dst = p.local_q + (size_t)row * qrow_bytes;
+          bulk_store(dst + voff, my_piece, kBN / 2);
+          bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
+        }
+        if (p.nranks) {
+          if (p.two_shot) {
+            char* dst = p.win[row % p.nranks] + buf_off + ((size_t)p.rank * p.capo + row / p.nranks) * kRecStride;
+            bulk_store(dst + voff, my_piece, kBN / 2);
+            bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
+          } else {
+            for (int d = 0; d < p.nranks; d++) {
+              char* dst = p.win[d] + buf_off + ((size_t)p.rank * p.cap + row) * kRecStride;
+              bulk_store(dst + voff, my_piece, kBN / 2);
+              bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
+            }
+          }
+        }
+      }
+      bulk_commit();
+      __syncwarp();
+    }
+    bulk_wait_done<0>();
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+// ---- host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+static bool make_map(CUtensorMap* m, const void* base, int rows, int k, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static StatusWords* gemm_status_word() {
+  static StatusWords* p[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!p[dev]) {
+    if (cudaMalloc(&p[dev], sizeof(StatusWords)) != cudaSuccess) return nullptr;
+    cudaMemset(p[dev], 0, sizeof(StatusWords));
+  }
+  return p[dev];
+}
+
+}  // namespace fp4ar
+
+using namespace fp4ar;
+
+extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, const void* wt, int M, int N,
+                                int K, float gs, void* local_q, float* dbg_acc, fp4ar_stream stream) {
+  if (!x || !wt || M < 1 || N < kBN || K < kBK || (N % kBN) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
+  if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
+  if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.inv_gs = 1.0f / gs;
+  p.local_q = (char*)local_q; p.dbg_acc = dbg_acc;
+  if (push) {
+    if (N != FP4AR_HIDDEN || push->nranks < 1 || push->nranks > FP4AR_MAX_RANKS || !push->call_counter) return FP4AR_ERR_ARGUMENT;
+    if (M > push->cap) return FP4AR_ERR_ARGUMENT;
+    p.nranks = push->nranks; p.rank = push->rank; p.cap = push->cap; p.capo = push->capo;
+    p.buf_bytes = push->buffer_bytes; p.call_counter = push->call_counter; p.two_shot = two_shot ? 1 : 0;
+    for (int r = 0; r < push->nranks; r++) {
+      if (!push->windows[r]) return FP4AR_ERR_ARGUMENT;
+      p.win[r] = (char*)push->windows[r];
+    }
+    // host-side bound of the farthest byte this call can touch in a window
+    const size_t last = two_shot ? ((size_t)(p.nranks - 1) * p.capo + (size_t)(M - 1) / p.nranks + 1) * kRecStride
+                                 : ((size_t)(p.nranks - 1) * p.cap + (size_t)M) * kRecStride;
+    if (last > p.buf_bytes) return FP4AR_ERR_ARGUMENT;
+  }
+  p.status = gemm_status_word();
+  if (!p.status) return cuda_fail();
+  p.timeout_ns = 2000000000ull;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, kBN)) return FP4AR_ERR_UNSUPPORTED;
+  if (cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess) return cuda_fail();
+  const int tiles = (N / kBN) * ((M + kBM - 1) / kBM);
+  const int sms = device_sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_nvfp4_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(ma, mb, p);
+  return cuda_check_launch();
+}
+
+extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {
+  StatusWords* s = gemm_status_word();
+  if (!s || !out) return FP4AR_ERR_ARGUMENT;
+  if (cudaMemcpy(out, s, sizeof(StatusWords), cudaMemcpyDeviceToHost) != cudaSuccess) return cuda_fail();
+  return FP4AR_OK;
+}

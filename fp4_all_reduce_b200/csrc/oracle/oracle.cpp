@@ -256,6 +256,31 @@ void fp4ar_oracle_encode_static(const uint16_t* x, int rows, float gs, uint8_t* 
   }
 }
 
+// FP32 rows with a static scale (what the GEMM epilogue does to its accumulators); `cols` per row, multiple of 16.
+void fp4ar_oracle_encode_static_f32(const float* x, int rows, int cols, float gs, uint8_t* v, long v_stride, uint8_t* s,
+                                    long s_stride) {
+  const float inv = 1.0f / gs;
+#pragma omp parallel for
+  for (int r = 0; r < rows; r++) {
+    const float* f = x + (size_t)r * cols;
+    uint8_t* vr = v + (size_t)r * v_stride;
+    uint8_t* sr = s + (size_t)r * s_stride;
+    for (int b = 0; b < cols / 16; b++) {
+      const float bm = absmax(f + 16 * b, 16);
+      const uint8_t sb = e4m3_encode((bm * inv) / 6.0f);
+      sr[b] = sb;
+      const float sff = g_e4m3_val[sb];
+      const float m = sff > 0.f ? inv / sff : 0.f;
+      for (int i = 0; i < 16; i += 2) {
+        uint8_t n0 = e2m1_encode(f[16 * b + i] * m), n1 = e2m1_encode(f[16 * b + i + 1] * m);
+        if (n0 == 8) n0 = 0;
+        if (n1 == 8) n1 = 0;
+        vr[(16 * b + i) >> 1] = (uint8_t)(n0 | (n1 << 4));
+      }
+    }
+  }
+}
+
 // acc[rows][H] (FP32) += decode of one source; call once per source in rank order, acc starting at +0.
 void fp4ar_oracle_decode_acc(float* acc, int rows, const uint8_t* v, long v_stride, const uint8_t* s, long s_stride,
                              const float* rs, float rs_static) {

@@ -109,6 +109,17 @@ def encode_static(x_bits: np.ndarray, gs: float) -> np.ndarray:
     return q
 
 
+def encode_static_f32(x: np.ndarray, gs: float) -> np.ndarray:
+    """[rows, cols] FP32 -> NVFP4 rows [rows, cols/2 + cols/16] with the static scale gs (the GEMM epilogue's quantiser)."""
+    x = _c(x, np.float32)
+    rows, cols = x.shape
+    q = np.empty((rows, cols // 2 + cols // 16), np.uint8)
+    base = q.ctypes.data
+    N.oracle().fp4ar_oracle_encode_static_f32(_p(x), rows, cols, C.c_float(gs), C.c_void_p(base), q.shape[1],
+                                              C.c_void_p(base + cols // 2), q.shape[1])
+    return q
+
+
 def decode_acc(acc: np.ndarray, v: np.ndarray, s: np.ndarray, rs) -> np.ndarray:
     """acc [rows,6144] f32 += decode(v, s, rs); rs is an array of row scales or one static scale."""
     assert acc.dtype == np.float32 and acc.flags.c_contiguous

@@ -1,0 +1,69 @@
+"""The tcgen05 GEMM with NVFP4 epilogue: accumulators against an FP32 matmul, quantised rows bit for bit
+against the host quantiser applied to the kernel's own accumulators, and the fused GEMM -> push -> AllReduce
+path on emulated ranks against the host model fed with the kernel's NVFP4 partials."""
+import numpy as np
+import pytest
+import torch
+
+from fp4_all_reduce_b200 import _native as N
+from fp4_all_reduce_b200 import oracle as O
+from fp4_all_reduce_b200.ops import gemm as G
+from fp4_all_reduce_b200.parallel.context import EmulatedGroup, make_args
+from fp4_all_reduce_b200.utils import data as D
+
+pytestmark = pytest.mark.gpu
+
+
+def _xw(M, K, Nn, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    wt = (torch.randn(Nn, K, generator=g) / K ** 0.5).to(torch.bfloat16).cuda()
+    return x, wt
+
+
+@pytest.mark.parametrize("M,K,Nn", [(128, 64, 256), (300, 512, 512), (1024, 2048, 6144), (77, 4096, 6144)])
+def test_gemm_accumulators_and_quantised_rows(M, K, Nn):
+    x, wt = _xw(M, K, Nn, 1)
+    gs = G.calibrate_gs(x, wt)
+    q, acc = G.gemm_nvfp4(x, wt, gs, want_acc=True)
+    torch.cuda.synchronize()
+    assert G.gemm_status().code == 0
+    ref = x.float() @ wt.float().t()
+    err = (acc - ref).abs().max().item()
+    assert err <= 2e-3 * ref.abs().max().item() + 1e-4, err
+    want = O.encode_static_f32(acc.cpu().numpy(), gs)
+    assert np.count_nonzero(q.cpu().numpy() != want) == 0
+
+
+@pytest.mark.parametrize("P", [2, 4])
+def test_gemm_push_then_allreduce_on_emulated_ranks(P):
+    M, K = 256, 512
+    g = EmulatedGroup(P, M)
+    g.set_timeout_ms(500)
+    xs, wts, gss, qs = [], [], [], []
+    for r in range(P):
+        x, wt = _xw(M, K, N.HIDDEN, 10 + r)
+        xs.append(x); wts.append(wt)
+        gss.append(G.calibrate_gs(x, wt))
+    res = [D.residual(M).cuda() for _ in range(P)]
+    res0 = res[0].clone()
+    w = D.norm_weight().cuda()
+    outs = [torch.zeros(M, N.HIDDEN, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
+    for call in range(3):                       # three calls: both window buffers and a reuse
+        for r in range(P):
+            res[r].copy_(res0)
+            lq = torch.empty(M, N.QROW_BYTES, dtype=torch.uint8, device="cuda")
+            G.gemm_push(g, xs[r], wts[r], gss[r], two_shot=P > 2, local_rank=r, local_q=lq)
+            qs.append(lq)
+        g.launch([make_args(x=None, out=outs[r], rows=M, input=N.IN_PUSHED, gs=gss, epilogue=N.EPI_NORM_BF16,
+                            res_in=res[r], res_out=res[r], weight=w,
+                            algo=N.ALGO_TWOSHOT if P > 2 else N.ALGO_ONESHOT) for r in range(P)])
+        torch.cuda.synchronize()
+        assert g.status(0).ok, g.status(0).describe()
+        partials = [t.cpu().numpy() for t in qs[-P:]]
+        exp = O.allreduce(partials, algo=1 if P > 2 else 0, input_kind=1, gs=gss, epi=1, res_in=O.bf16_bits(res0),
+                          weight=O.bf16_bits(w))
+        for r in range(P):
+            assert np.array_equal(O.bf16_bits(outs[r]), exp["out"]), (call, r)
+            assert np.array_equal(O.bf16_bits(res[r]), exp["res_out"]), (call, r)
+    g.close()
