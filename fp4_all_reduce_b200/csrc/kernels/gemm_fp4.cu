@@ -113,6 +113,18 @@ __device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile) {
 // Instruction descriptor: D = F32, A = B = BF16, both K-major, N = 256, M = 128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 
+// Tile order: the N tiles are walked in panels of kPanel; inside a panel consecutive tile indices step through
+// N fastest and then M.  The ~148 tiles in flight at a time then cover about 18 row blocks x 8 column tiles, which
+// needs (18 + 2*8) * 128 * K * 2 bytes of operands from L2 instead of (6 + 2*24) for a plain row-major walk.
+constexpr int kPanel = 8;
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m0, int& n0) {
+  const int per_panel = m_tiles * kPanel;
+  const int panel = t / per_panel, within = t - panel * per_panel;
+  const int width = min(kPanel, n_tiles - panel * kPanel);
+  const int m = within / width, n = panel * kPanel + within % width;
+  m0 = m * kBM; n0 = n * kBN;
+}
+
 struct GemmWait {
   volatile uint32_t* abort_flag;
   StatusWords* status;
@@ -176,7 +188,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * kBN;
+        int m0, n0;
+        tile_coords(t, m_tiles, n_tiles, m0, n0);
         for (int kb = 0; kb < kblocks; kb++, it++) {
           const int s = it % kStages;
           if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
@@ -226,7 +239,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const int qrow_bytes = p.N / 2 + p.N / 16;
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
-      const int m0 = (t / n_tiles) * kBM, n0 = (t % n_tiles) * kBN;
+      int m0, n0;
+      tile_coords(t, m_tiles, n_tiles, m0, n0);
       const uint32_t a = tile_i & 1u;
       const int row = m0 + r_in_tile;
       // warp-uniform verdict: the tcgen05.ld below is a warp-wide instruction
