@@ -1,0 +1,71 @@
+"""Build the reference project's own kernels, untouched, for sm_100a, plus the driver that calls them.
+
+    python baseline/build_ref.py [--src /path/to/reference]
+
+Copies the reference tree to baseline/_ref/src (that directory is not tracked), compiles
+kernels/push/tp2_l2.cu (variant L2, -DLAMPORT_V2=1), kernels/push/tp4_l4.cu (variant L4) and
+kernels/fused_norm/lnorm.cu exactly the way the reference's build.sh:18-31 does (same flags, same
+-DFP4AR_NAME / -DFP4AR_REGISTER defines), and links them with baseline/ref_shim.cu into baseline/_ref/ref_shim.
+The reference's harness itself cannot be linked here: it needs ncclGetLsaDevicePointer (NCCL >= 2.31).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+
+
+def nccl_paths():
+    import nvidia
+    base = Path(list(nvidia.__path__)[0]) / "nccl"
+    return base / "include", base / "lib"
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--src", default="/root/reference")
+    ns = ap.parse_args(argv)
+    src = OUT / "src"
+    if Path(ns.src).exists():
+        if src.exists():
+            shutil.rmtree(src)
+        shutil.copytree(ns.src, src, ignore=shutil.ignore_patterns(".git"))
+    if not src.exists():
+        print("reference sources not found", file=sys.stderr)
+        return 1
+    inc, lib = nccl_paths()
+    nv = ["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+          f"-I{src}/include", f"-I{src}/harness", f"-I{src}/kernels/fused_norm", f"-I{inc}"]
+    jobs = [
+        (["-DLAMPORT_V2=1", "-DFP4AR_NAME=L2", "-DFP4AR_REGISTER=fp4ar_register_L2", "-c", f"{src}/kernels/push/tp2_l2.cu"], OUT / "v_L2.o"),
+        (["-DFP4AR_NAME=L4", "-DFP4AR_REGISTER=fp4ar_register_L4", "-c", f"{src}/kernels/push/tp4_l4.cu"], OUT / "v_L4.o"),
+        (["-c", f"{src}/kernels/fused_norm/lnorm.cu"], OUT / "lnorm.o"),
+        (["-c", str(HERE / "ref_shim.cu")], OUT / "ref_shim.o"),
+    ]
+    procs = [(subprocess.Popen(nv + a + ["-o", str(o)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), o) for a, o in jobs]
+    ok = True
+    for p, o in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            ok = False
+            print(f"FAILED {o.name}\n{out[-3000:]}")
+    if not ok:
+        return 1
+    link = ["nvcc", "-o", str(OUT / "ref_shim")] + [str(o) for _, o in jobs] + [f"-L{lib}", "-l:libnccl.so.2", "-lpthread", "-ldl",
+            "-Xlinker", f"-rpath={lib}", "-gencode", "arch=compute_100a,code=sm_100a"]
+    r = subprocess.run(link, capture_output=True, text=True)
+    if r.returncode != 0:
+        print(r.stdout, r.stderr)
+        return 1
+    print(OUT / "ref_shim")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -31,12 +31,41 @@ PUBLISHED_AR_US = {2: {1024: 10.8, 2048: 15.2, 4096: 21.9, 8192: 34.4, 16384: 60
                    4: {1024: 19.8, 2048: 25.6, 4096: 34.8, 8192: 56.2, 16384: 103.8}}
 
 
-def reference_arm(args) -> int:
-    """The reference cannot run here: say why in one line and exit 0."""
-    why = ("reference is not installable (no setup.py/pyproject; pip: 'Neither setup.py nor pyproject.toml found') "
-           "and its harness needs ncclGetLsaDevicePointer from NCCL >= 2.31 while this image ships NCCL 2.28.9")
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+def reference_arm(ns) -> int:
+    """The reference's own fused block kernel (kernels/fused_norm/lnorm.cu, untouched, built by
+    baseline/build_ref.py) timed with the same protocol: a graph of 121 blocks, device-timed, max over ranks.
+    The reference implements the fused block for 2 ranks (and a one-shot form for 4); other sizes are unavailable.
+    Its ranks run as threads of ONE process (the reference harness's model), so rank 0 launches the driver and the
+    other torchrun ranks only wait."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    rec = None
+    if rank == 0:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        try:
+            import reference_arm as RA
+            if world not in (2, 4):
+                rec = {"impl": "reference", "unavailable": f"the reference's fused AllReduce+norm kernel exists for 2 (and 4) ranks, not {world}"}
+            else:
+                r = RA.run_shim(["--tp", world, "--variant", "lnorm", "--epi", 1, "--rows", ns.rows, "--graph", 121,
+                                 "--iters", max(ns.steps, 1), "--warmup", max(ns.warmup, 3)], timeout=600)
+                if "unavailable" in r:
+                    rec = r
+                else:
+                    pub = PUBLISHED_BLOCK_US.get(world, {}).get(ns.rows)
+                    rec = {"metric": "us/call (graph, max over ranks) 6144-wide AR+residual+RMSNorm block", "impl": "reference",
+                           "value": round(r["med_us"], 3), "unit": "us/call", "n_gpus": world, "steps": ns.steps,
+                           "warmup": max(ns.warmup, 3), "ms_per_step": round(r["med_us"] * 121 / 1000.0, 4),
+                           "higher_is_better": False, "scaling": "weak", "vs_baseline": round(r["med_us"] / pub, 4) if pub else None,
+                           "dtype": "bf16", "data": "synthetic",
+                           "config": {"model": "MiniMax-M3 prefill block chain (121 x AR+residual+GemmaRMSNorm, hidden 6144)",
+                                      "global_batch": ns.rows, "seq_len": ns.rows, "parallelism": f"tp{world}",
+                                      "kernel": "reference lnorm_kernel (one-shot push), driver baseline/ref_shim.cu",
+                                      "calls_per_graph": 121},
+                           "p10_us": r["p10_us"], "p90_us": r["p90_us"]}
+        except Exception as e:  # the arm must never take the benchmark down
+            rec = {"impl": "reference", "unavailable": f"driver failed: {type(e).__name__}: {str(e)[:200]}"}
+        print(json.dumps(rec), flush=True)
     return 0
 
 
