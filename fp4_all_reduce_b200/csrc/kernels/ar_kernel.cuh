@@ -61,17 +61,20 @@ struct ArParams {
 template <int P, int ALGO, int IN, int EPI, int T>
 struct ArShape {
   static constexpr int NJ = 6 / T;                                   // pairs per lane per row
-  static constexpr bool kHasX = IN == 0;
-  static constexpr bool kHasRes = EPI > 0;
-  static constexpr int NXB = (kHasX && kHasRes) ? 3 : ((kHasX || kHasRes) ? 2 : 0);
-  static constexpr int NREC = IN == 1 ? 3 : 2;
+  static constexpr bool kTwoShot = ALGO == 1 && P > 1;
+  // Rows are finished LAG steps after they were encoded: 1 for one-shot (every source pushed during the previous
+  // step), 2 for two-shot (the owner re-encodes and broadcasts during the step in between), so that a finishing
+  // team finds its data in place and the ranks need not run in lock step.
+  static constexpr int LAG = kTwoShot ? 2 : 1;
+  static constexpr int NXB = IN == 0 ? 2 : 0;                        // x row buffers (the residual never sits in shared memory)
+  static constexpr int NREC = (IN == 1 ? 3 : 2) + (kTwoShot ? 1 : 0);
   static constexpr int kOutBytes = EPI <= 1 ? kRowBytes : (EPI == 2 ? 3584 : 6400);
   static constexpr int kMisc = 128;                                  // mbarriers + reduction scratch
   static constexpr int kTeamBytes = NXB * kRowBytes + kOutBytes + NREC * kRecStride + kMisc;
   static constexpr int kCtaExtra = kRecStride + 128;                 // sentinel record + abort flag
   static constexpr int NSG = IN == 2 ? P : P - 1;                    // sources read from the window
-  // Two-shot owners hold a whole FP32 row slice in registers and the norm epilogue holds BF16 z:
-  // those shapes get fewer, fatter threads.
+  // Two-shot owners hold a whole FP32 row slice in registers and the norm epilogue holds BF16 z and the
+  // residual: those shapes get fewer, fatter threads.
   // (Register budget per thread = 65536 / (32 * T * kMaxTeams).)
   static constexpr int kHeavy = (ALGO == 1 || EPI > 0) ? 1 : 0;
   static constexpr int kMaxTeams = T == 2 ? (kHeavy ? 6 : 8) : (T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : 3));
@@ -135,7 +138,8 @@ struct TeamSync {
 template <int P, int ALGO, int IN, int EPI, int T>
 __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTeams, 1) ar_kernel(const __grid_constant__ ArParams prm) {
   using S = ArShape<P, ALGO, IN, EPI, T>;
-  constexpr int NJ = S::NJ, NXB = S::NXB, NREC = S::NREC, NSG = S::NSG;
+  constexpr int NJ = S::NJ, NXB = S::NXB, NREC = S::NREC, NSG = S::NSG, LAG = S::LAG;
+  constexpr bool kTwoShot = S::kTwoShot;
   constexpr int NXB1 = NXB > 0 ? NXB : 1;   // keeps index arithmetic well-formed in shapes without row buffers
   extern __shared__ __align__(1024) uint8_t smem[];
 
@@ -153,13 +157,12 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
 
   // ---- shared-memory carve-up ----
   uint8_t* tbase = smem + (size_t)team * S::kTeamBytes;
-  uint8_t* xb = tbase;                                   // NXB row buffers (x rows, residual rows, res_out staging)
+  uint8_t* xb = tbase;                                   // NXB buffers for BF16 input rows
   uint8_t* outst = tbase + NXB * kRowBytes;              // output staging row
   uint8_t* recs = outst + S::kOutBytes;                  // NREC encoded records
   uint64_t* xbar = reinterpret_cast<uint64_t*>(recs + NREC * kRecStride);  // [3] x loads
-  uint64_t* rbar = xbar + 3;                             // [3] residual loads
-  uint64_t* qbar = rbar + 3;                             // [3] NVFP4 record loads
-  float* red = reinterpret_cast<float*>(qbar + 3);       // [2][6] reduction exchange
+  uint64_t* qbar = xbar + 2;                             // [4] NVFP4 record loads
+  float* red = reinterpret_cast<float*>(qbar + 4);       // [2][6] reduction exchange
   uint8_t* sentinel = smem + (size_t)nteams * S::kTeamBytes;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sentinel + kRecStride);
   const TeamSync<T> tsync{1 + team};
@@ -168,7 +171,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   if (threadIdx.x == 0) *abort_flag = 0u;
   if (leader) {
 #pragma unroll
-    for (int i = 0; i < 9; i++) mbar_init(xbar + i, 1);
+    for (int i = 0; i < 6; i++) mbar_init(xbar + i, 1);
   }
   for (int i = threadIdx.x; i < kRecStride / 16; i += blockDim.x) {
     uint4 v;
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     if (IN == 0) {
       mbar_arrive_expect(xbar + 0, kRowBytes);
       bulk_load(xb, io.x + (size_t)row_of(0) * kRowBytes, kRowBytes, xbar + 0);
-      if (EPI == 0 && nk > 1) {
+      if (nk > 1) {
         mbar_arrive_expect(xbar + 1, kRowBytes);
         bulk_load(xb + kRowBytes, io.x + (size_t)row_of(1) * kRowBytes, kRowBytes, xbar + 1);
       }
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   // order; this routine applies the epilogue, stages the row and lets the leader store it.
   // `leader_extra()` issues the leader's other stores of this row (re-arm, broadcast).
   // =============================================================================================
-  auto finish_row = [&](int k1, int row, auto&& fill, auto&& leader_extra) {
+  auto finish_row = [&](int row, auto&& fill, auto&& leader_extra) {
     const int pbase = tw;  // pair of (lane, j) = lane + 32 * (tw + T * j)
     if constexpr (EPI == 0) {
 #pragma unroll
@@ -255,8 +258,18 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
         leader_extra();
       }
     } else {
-      uint8_t* resbuf = xb + (k1 % NXB1) * kRowBytes;
-      mbar_wait_bounded(rbar + (k1 % NXB1), (uint32_t)((k1 / NXB1) & 1), wctx, row);
+      // The residual row is read straight from global memory into registers (issued before the window data is
+      // polled and decoded, so its latency is hidden) and the updated residual is written straight back: each lane
+      // touches whole 64-byte pieces, so every 32-byte sector it reads or writes is fully used.
+      const char* res_row = io.res_in + (size_t)row * kRowBytes;
+      char* res_out_row = io.res_out + (size_t)row * kRowBytes;
+      uint4 rr[NJ][4];
+#pragma unroll
+      for (int j = 0; j < NJ; j++) {
+        const int p = lane + 32 * (pbase + T * j);
+#pragma unroll
+        for (int k = 0; k < 4; k++) rr[j][k] = *reinterpret_cast<const uint4*>(res_row + p * 64 + ((k ^ f) << 4));
+      }
       uint4 zb[NJ][4];
       float gsum[NJ];
 #pragma unroll
@@ -264,22 +277,15 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
         const int p = lane + 32 * (pbase + T * j);
         float acc[32];
         fill(j, acc);
-        uint4 r[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) r[k] = lds16(resbuf + p * 64 + ((k ^ f) << 4));
-        const float sp = add_residual_sumsq(acc, r);
+        const float sp = add_residual_sumsq(acc, rr[j]);
         pack32_bf16(acc, zb[j]);
 #pragma unroll
-        for (int k = 0; k < 4; k++) sts16(resbuf + p * 64 + ((k ^ f) << 4), zb[j][k]);
+        for (int k = 0; k < 4; k++) *reinterpret_cast<uint4*>(res_out_row + p * 64 + ((k ^ f) << 4)) = zb[j][k];
         gsum[j] = warp_sum_butterfly(sp);
       }
-      fence_smem_to_async();
       float g6[6];
-      team_gather6(gsum, g6);   // also: every lane's z is in resbuf, every lane is done polling
-      if (leader) {
-        bulk_store(io.res_out + (size_t)row * kRowBytes, resbuf, kRowBytes);
-        leader_extra();
-      }
+      team_gather6(gsum, g6);   // also: every lane is done polling, so the slots may be re-armed
+      if (leader) leader_extra();
       float ss = g6[0];
 #pragma unroll
       for (int g = 1; g < 6; g++) ss = __fadd_rn(ss, g6[g]);
@@ -364,104 +370,107 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   auto window_source = [&](int i) { return IN == 2 ? i : i + (i >= me ? 1 : 0); };
 
   // =============================================================================================
-  // main pipeline
+  // main pipeline.  Step k: (two-shot) owner step of row k-1; encode + push row k; finish row k-LAG.
   // =============================================================================================
 #ifdef FP4AR_PHASE_TIMERS
   long long phase_t0_ = clock64();
 #endif
-  for (int k = 0; k <= nk; k++) {
+  constexpr int kPfSrc = NSG > 0 ? NSG : 1;
+  constexpr bool kPfAll = NJ * NSG <= 8;            // a whole row of every window source fits in registers
+  auto settle_rs = [&](uint32_t bits, const char* rec, int row, int src, int phase) -> float {
+    return rowscale_pending(bits) ? poll_rowscale(rec, row, src, phase) : __uint_as_float(bits);
+  };
+
+  for (int k = 0; k < nk + LAG; k++) {
     FP4AR_PHASE(0);
-#ifdef FP4AR_EXPERIMENT_WAIT1
-    if (leader) bulk_wait_source_free<1>();
-#else
     if (leader) bulk_wait_source_free<0>();
-#endif
     tsync.sync();
     FP4AR_PHASE(1);   // drain wait + barrier
-    if (leader && k < nk) {
-      if (IN == 0 && EPI > 0 && k + 1 < nk) {
-        const int b = (k + 1) % 3;
-        mbar_arrive_expect(xbar + b, kRowBytes);
-        bulk_load(xb + b * kRowBytes, io.x + (size_t)row_of(k + 1) * kRowBytes, kRowBytes, xbar + b);
-      }
-      if (IN == 1 && k + 1 < nk) {
-        const int b = (k + 1) % 3;
-        mbar_arrive_expect(qbar + b, kQRowBytes);
-        bulk_load(recs + b * kRecStride, io.x + (size_t)row_of(k + 1) * kQRowBytes, kQRowBytes, qbar + b);
-      }
-      if (IN != 0 && EPI > 0) {
-        const int b = k % 2;
-        mbar_arrive_expect(rbar + b, kRowBytes);
-        bulk_load(xb + b * kRowBytes, io.res_in + (size_t)row_of(k) * kRowBytes, kRowBytes, rbar + b);
-      }
+    if (leader && IN == 1 && k + 1 < nk) {
+      const int b = (k + 1) % NREC;
+      mbar_arrive_expect(qbar + b, kQRowBytes);
+      bulk_load(recs + b * kRecStride, io.x + (size_t)row_of(k + 1) * kQRowBytes, kQRowBytes, qbar + b);
     }
 
-    // ------------------------------------------------------------------ early window loads of row k-1
-    // One-shot rows and rows this rank owns: every source pushed its record during the previous step, so the
-    // loads are issued now and their latency overlaps what follows; stage B validates them and falls back to
-    // polling for whatever had not arrived.  Rows owned by a peer: that peer re-encodes the row during this very
-    // step (before it encodes its own row k), so their loads are issued after stage A.
-    constexpr int kPfSrc = NSG > 0 ? NSG : 1;
-    constexpr bool kPfAll = NJ * NSG <= 8;            // a whole row of every window source fits in registers
-    constexpr int kPfData = kPfAll ? kPfSrc : 1;
-    constexpr bool kTwoShot = ALGO == 1 && P > 1;
-    const char* psrc[kPfSrc];
-    uint32_t prs[kPfSrc];
-    uint4 pq[NJ][kPfData];
-    uint32_t psf[NJ][kPfData];
-    bool row1_owned = false, row1_has_rs = false;
-    float row1_rs2 = 0.0f;                            // row scale of the re-encoding of an owned row
-    if (k >= 1) {
-      const int row1 = row_of(k - 1);
+    // ------------------------------------------------------------------ early window loads
+    // (a) the row finished in this step (k - LAG): one-shot sources, or the owner's broadcast of a row owned by a peer;
+    // (b) two-shot: the reduce-scatter sources of row k-1 when this rank owns it.
+    // Everything was pushed at least one full step ago; stage-specific code validates and falls back to polling.
+    const int kf = k - LAG;                          // row index (in this team's sequence) finished in this step
+    const bool fin = kf >= 0 && kf < nk;
+    const int frow = fin ? row_of(kf) : 0;
+    const bool fin_owned = kTwoShot && fin && (frow % P) == me;
+    const char* fsrc[kTwoShot ? 1 : kPfSrc];
+    uint32_t frs[kTwoShot ? 1 : kPfSrc];
+    uint4 fq[NJ][kTwoShot ? 1 : (kPfAll ? kPfSrc : 1)];
+    uint32_t fsf[NJ][kTwoShot ? 1 : (kPfAll ? kPfSrc : 1)];
+    bool f_has_rs = false;
+    if (fin) {
       if constexpr (!kTwoShot) {
 #pragma unroll
-        for (int i = 0; i < NSG; i++) psrc[i] = my_buf + os_slot(window_source(i), row1);
-        row1_has_rs = IN == 0;
-      } else {
-        row1_owned = (row1 % P) == me;
-        if (row1_owned) {
-#pragma unroll
-          for (int i = 0; i < NSG; i++) psrc[i] = my_buf + rs_slot(window_source(i), row1);
-          row1_has_rs = IN == 0;
-        } else {
-          psrc[0] = my_buf + ag_slot(row1 % P, row1);
-          row1_has_rs = !(loopb && IN >= 1);
-        }
-      }
-      if (!kTwoShot || row1_owned) {
+        for (int i = 0; i < NSG; i++) fsrc[i] = my_buf + os_slot(window_source(i), frow);
+        f_has_rs = IN == 0;
 #pragma unroll
         for (int i = 0; i < NSG; i++)
-          if (row1_has_rs) prs[i] = poll_ld4(psrc[i] + kQRowBytes);
+          if (f_has_rs) frs[i] = poll_ld4(fsrc[i] + kQRowBytes);
         if (kPfAll) {
 #pragma unroll
           for (int jj = 0; jj < NJ; jj++) {
             const int p = lane + 32 * (tw + T * jj);
 #pragma unroll
             for (int i = 0; i < NSG; i++) {
-              pq[jj][i] = poll_ld16(psrc[i] + 16 * p);
-              psf[jj][i] = poll_ld2(psrc[i] + kValueBytes + 2 * p);
+              fq[jj][i] = poll_ld16(fsrc[i] + 16 * p);
+              fsf[jj][i] = poll_ld2(fsrc[i] + kValueBytes + 2 * p);
             }
           }
         }
+      } else if (!fin_owned) {
+        fsrc[0] = my_buf + ag_slot(frow % P, frow);
+        f_has_rs = !(loopb && IN >= 1);
+        if (f_has_rs) frs[0] = poll_ld4(fsrc[0] + kQRowBytes);
+#pragma unroll
+        for (int jj = 0; jj < NJ; jj++) {
+          const int p = lane + 32 * (tw + T * jj);
+          fq[jj][0] = poll_ld16(fsrc[0] + 16 * p);
+          fsf[jj][0] = poll_ld2(fsrc[0] + kValueBytes + 2 * p);
+        }
       }
     }
-    auto settle_rs = [&](uint32_t bits, const char* rec, int row, int src, int phase) -> float {
-      return rowscale_pending(bits) ? poll_rowscale(rec, row, src, phase) : __uint_as_float(bits);
-    };
-
     FP4AR_PHASE(2);   // early loads issued
+
     // ------------------------------------------------------------------ owner step of row k-1 (two-shot)
-    // Reduce every source, re-encode, broadcast.  It runs before this rank encodes row k so that the peers,
-    // which encode their row k meanwhile, find the broadcast when they turn to row k-1.
+    // Reduce every source, re-encode into rec, broadcast.  The row is finished (decoded, epilogue) one step later
+    // like every other row, from the record kept in the ring.
     if constexpr (kTwoShot) {
-      if (k >= 1 && row1_owned) {
-        const int row = row_of(k - 1);
-        uint8_t* rec_own = recs + ((k - 1) % NREC) * kRecStride;
+      const int ko = k - 1;
+      if (ko >= 0 && ko < nk && (row_of(ko) % P) == me) {
+        const int row = row_of(ko);
+        uint8_t* rec_own = recs + (ko % NREC) * kRecStride;
+        const char* osrc[kPfSrc];
         float wrs[kPfSrc];
+        uint32_t ors[kPfSrc];
+#pragma unroll
+        for (int i = 0; i < NSG; i++) {
+          osrc[i] = my_buf + rs_slot(window_source(i), row);
+          if (IN == 0) ors[i] = poll_ld4(osrc[i] + kQRowBytes);
+        }
+        uint4 oq[NJ][kPfAll ? kPfSrc : 1];
+        uint32_t osf[NJ][kPfAll ? kPfSrc : 1];
+        if (kPfAll) {
+#pragma unroll
+          for (int jj = 0; jj < NJ; jj++) {
+            const int p = lane + 32 * (tw + T * jj);
+#pragma unroll
+            for (int i = 0; i < NSG; i++) {
+              oq[jj][i] = poll_ld16(osrc[i] + 16 * p);
+              osf[jj][i] = poll_ld2(osrc[i] + kValueBytes + 2 * p);
+            }
+          }
+        }
 #pragma unroll
         for (int i = 0; i < NSG; i++) {
           const int s = window_source(i);
-          wrs[i] = IN == 0 ? settle_rs(prs[i], psrc[i], row, s, 2) : prm.gs[s];
+          wrs[i] = IN == 0 ? settle_rs(ors[i], osrc[i], row, s, 2) : prm.gs[s];
         }
         float own_rs = 0.0f;
         if (IN == 0) own_rs = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
@@ -475,12 +484,12 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           uint32_t wsf[kPfSrc];
 #pragma unroll
           for (int i = 0; i < NSG; i++) {
-            if (kPfAll) { wq[i] = pq[j][i]; wsf[i] = psf[j][i]; }
-            else { wq[i] = poll_ld16(psrc[i] + 16 * p); wsf[i] = poll_ld2(psrc[i] + kValueBytes + 2 * p); }
+            if (kPfAll) { wq[i] = oq[j][i]; wsf[i] = osf[j][i]; }
+            else { wq[i] = poll_ld16(osrc[i] + 16 * p); wsf[i] = poll_ld2(osrc[i] + kValueBytes + 2 * p); }
           }
 #pragma unroll
           for (int i = 0; i < NSG; i++)
-            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(psrc[i], p, wq[i], wsf[i], row, window_source(i), 2);
+            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(osrc[i], p, wq[i], wsf[i], row, window_source(i), 2);
           zero32(sums[j]);
           if (!xport) {
 #pragma unroll
@@ -505,7 +514,6 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
         }
         const RowScale sc = row_scale_from_amax(am);
-        row1_rs2 = sc.rs;
         if (!xport) {
 #pragma unroll
           for (int j = 0; j < NJ; j++) {
@@ -521,15 +529,15 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
             const uint32_t rb4 = __float_as_uint(sc.rs);
             sts16(rec_own + kQRowBytes, make_uint4(rb4, rb4, rb4, rb4));
           }
-        } else if (IN == 2) {
+        } else {
+          if (IN == 2) {
 #pragma unroll
-          for (int j = 0; j < NJ; j++) {
-            const int p = lane + 32 * (tw + T * j);
-            sts16(rec_own + 16 * p, make_uint4(0x11111111u, 0x11111111u, 0x11111111u, 0x11111111u));
-            *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)0x3838u;
+            for (int j = 0; j < NJ; j++) {
+              const int p = lane + 32 * (tw + T * j);
+              sts16(rec_own + 16 * p, make_uint4(0x11111111u, 0x11111111u, 0x11111111u, 0x11111111u));
+              *reinterpret_cast<uint16_t*>(rec_own + kValueBytes + 2 * p) = (uint16_t)0x3838u;
+            }
           }
-          if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
-        } else if (IN == 1) {
           if (leader) sts16(rec_own + kQRowBytes, make_uint4(0x3f800000u, 0x3f800000u, 0x3f800000u, 0x3f800000u));
         }
         fence_smem_to_async();
@@ -542,13 +550,13 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
             bulk_store(dst, rec_own, kRecPayload);
           }
 #pragma unroll
-          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(psrc[i]), sentinel, kRecPayload);
+          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(osrc[i]), sentinel, kRecPayload);
         }
       }
     }
-
     FP4AR_PHASE(3);   // owner step
-    // ------------------------------------------------------------------ stage A: row k
+
+    // ------------------------------------------------------------------ stage A: encode + push row k
     if (k < nk) {
       const int row = row_of(k);
       uint8_t* rec = recs + (k % NREC) * kRecStride;
@@ -616,13 +624,13 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
         fence_smem_to_async();
         tsync.sync();
       } else if (IN == 1) {
-        mbar_wait_bounded(qbar + (k % 3), (uint32_t)((k / 3) & 1), wctx, row);
+        mbar_wait_bounded(qbar + (k % NREC), (uint32_t)((k / NREC) & 1), wctx, row);
       }
 
       if (leader) {
         if (IN != 2) {
           const uint32_t bytes = IN == 0 ? (uint32_t)kRecPayload : (uint32_t)kQRowBytes;
-          if (ALGO == 0) {
+          if (!kTwoShot) {
 #pragma unroll
             for (int d = 0; d < P; d++) {
               if (d == me) continue;
@@ -641,36 +649,26 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
             }
           }
         }
-        if (IN == 0) {
+        if (IN == 0 && k + 2 < nk) {
           const int b = k % NXB1;
-          if (EPI == 0) {
-            if (k + 2 < nk) {
-              mbar_arrive_expect(xbar + b, kRowBytes);
-              bulk_load(xb + b * kRowBytes, io.x + (size_t)row_of(k + 2) * kRowBytes, kRowBytes, xbar + b);
-            }
-          } else {
-            mbar_arrive_expect(rbar + b, kRowBytes);
-            bulk_load(xb + b * kRowBytes, io.res_in + (size_t)row * kRowBytes, kRowBytes, rbar + b);
-          }
+          mbar_arrive_expect(xbar + b, kRowBytes);
+          bulk_load(xb + b * kRowBytes, io.x + (size_t)row_of(k + 2) * kRowBytes, kRowBytes, xbar + b);
         }
       }
     }
-
     FP4AR_PHASE(6);   // encode pass 2 + push
-    // ------------------------------------------------------------------ stage B: finish row k-1
-    if (k >= 1) {
-      const int k1 = k - 1;
-      const int row = row_of(k1);
-      uint8_t* rec_own = recs + (k1 % NREC) * kRecStride;
-      const int owner = row % P;
 
+    // ------------------------------------------------------------------ stage B: finish row k - LAG
+    if (fin) {
+      const int row = frow;
+      uint8_t* rec_own = recs + (kf % NREC) * kRecStride;
       if constexpr (!kTwoShot) {
         // ---- one-shot: every rank decodes every source in rank order ----
         float wrs[kPfSrc];
 #pragma unroll
         for (int i = 0; i < NSG; i++) {
           const int s = window_source(i);
-          wrs[i] = IN == 0 ? settle_rs(prs[i], psrc[i], row, s, 1) : prm.gs[s];
+          wrs[i] = IN == 0 ? settle_rs(frs[i], fsrc[i], row, s, 1) : prm.gs[s];
         }
         float own_rs = 0.0f;
         if (IN == 0) own_rs = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
@@ -681,12 +679,12 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           uint32_t wsf[kPfSrc];
 #pragma unroll
           for (int i = 0; i < NSG; i++) {
-            if (kPfAll) { wq[i] = pq[j][i]; wsf[i] = psf[j][i]; }
-            else { wq[i] = poll_ld16(psrc[i] + 16 * p); wsf[i] = poll_ld2(psrc[i] + kValueBytes + 2 * p); }
+            if (kPfAll) { wq[i] = fq[j][i]; wsf[i] = fsf[j][i]; }
+            else { wq[i] = poll_ld16(fsrc[i] + 16 * p); wsf[i] = poll_ld2(fsrc[i] + kValueBytes + 2 * p); }
           }
 #pragma unroll
           for (int i = 0; i < NSG; i++)
-            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(psrc[i], p, wq[i], wsf[i], row, window_source(i), 1);
+            if (values_pending(wq[i]) | scales_pending(wsf[i])) poll_pair(fsrc[i], p, wq[i], wsf[i], row, window_source(i), 1);
           zero32(acc);
           if (!xport) {
 #pragma unroll
@@ -702,46 +700,40 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
         };
         auto extra = [&]() {
 #pragma unroll
-          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(psrc[i]), sentinel, kRecPayload);
+          for (int i = 0; i < NSG; i++) bulk_store(const_cast<char*>(fsrc[i]), sentinel, kRecPayload);
         };
-        finish_row(k1, row, fill, extra);
+        finish_row(row, fill, extra);
       } else {
-      if (owner == me) {
-        // ---- two-shot, owned row: its re-encoding sits in rec_own; every rank outputs the decode of that ----
-        auto fill = [&](int j, float* acc) {
-          const int p = lane + 32 * (tw + T * j);
-          zero32(acc);
-          if (!xport) {
-            const uint4 q = lds16(rec_own + 16 * p);
-            const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
-            decode_acc_lane(acc, q, sf2, row1_rs2, f);
-          }
-        };
-        auto extra = [&]() {};
-        finish_row(k1, row, fill, extra);
-      } else {
-        // ---- two-shot, row owned by a peer: wait for its broadcast and decode that single record ----
-        const char* src = psrc[0];
-        uint32_t rsb = 0;
-        if (row1_has_rs) rsb = poll_ld4(src + kQRowBytes);
-#pragma unroll
-        for (int jj = 0; jj < NJ; jj++) {
-          const int p = lane + 32 * (tw + T * jj);
-          pq[jj][0] = poll_ld16(src + 16 * p);
-          psf[jj][0] = poll_ld2(src + kValueBytes + 2 * p);
+        if (fin_owned) {
+          // ---- two-shot, owned row: its re-encoding sits in the ring; every rank outputs the decode of that ----
+          const float rs2 = *reinterpret_cast<const float*>(rec_own + kQRowBytes);
+          auto fill = [&](int j, float* acc) {
+            const int p = lane + 32 * (tw + T * j);
+            zero32(acc);
+            if (!xport) {
+              const uint4 q = lds16(rec_own + 16 * p);
+              const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(rec_own + kValueBytes + 2 * p);
+              decode_acc_lane(acc, q, sf2, rs2, f);
+            }
+          };
+          auto extra = [&]() {};
+          finish_row(row, fill, extra);
+        } else {
+          // ---- two-shot, row owned by a peer: its broadcast arrived during the previous step ----
+          const char* src = fsrc[0];
+          const int owner = row % P;
+          const float rs = f_has_rs ? settle_rs(frs[0], src, row, owner, 3) : prm.gs[me];
+          auto fill = [&](int j, float* acc) {
+            const int p = lane + 32 * (tw + T * j);
+            uint4 wq = fq[j][0];
+            uint32_t wsf = fsf[j][0];
+            if (values_pending(wq) | scales_pending(wsf)) poll_pair(src, p, wq, wsf, row, owner, 3);
+            zero32(acc);
+            if (!xport) decode_acc_lane(acc, wq, wsf, rs, f);
+          };
+          auto extra = [&]() { bulk_store(const_cast<char*>(src), sentinel, kRecPayload); };
+          finish_row(row, fill, extra);
         }
-        const float rs = row1_has_rs ? settle_rs(rsb, src, row, owner, 3) : prm.gs[me];
-        auto fill = [&](int j, float* acc) {
-          const int p = lane + 32 * (tw + T * j);
-          uint4 wq = pq[j][0];
-          uint32_t wsf = psf[j][0];
-          if (values_pending(wq) | scales_pending(wsf)) poll_pair(src, p, wq, wsf, row, owner, 3);
-          zero32(acc);
-          if (!xport) decode_acc_lane(acc, wq, wsf, rs, f);
-        };
-        auto extra = [&]() { bulk_store(const_cast<char*>(src), sentinel, kRecPayload); };
-        finish_row(k1, row, fill, extra);
-      }
       }
     }
     FP4AR_PHASE(7);   // finish
