@@ -55,6 +55,7 @@ struct ArParams {
   int rows, ctas_per_rank, flags;
   int cap, capo;
   unsigned long long buf_bytes, timeout_ns;
+  int lag_owner, lag_finish;          // two-shot pipeline depths in steps (1 <= lag_owner < lag_finish <= 4)
   unsigned long long* phase_cycles;   // tuning builds only (-DFP4AR_PHASE_TIMERS): 16 per-phase cycle counters
 };
 
@@ -65,9 +66,11 @@ struct ArShape {
   // Rows are finished LAG steps after they were encoded: 1 for one-shot (every source pushed during the previous
   // step), 2 for two-shot (the owner re-encodes and broadcasts during the step in between), so that a finishing
   // team finds its data in place and the ranks need not run in lock step.
-  static constexpr int LAG = kTwoShot ? 2 : 1;
+  // The two-shot lags are run-time parameters (owner step lag_o >= 1 steps after the encode, finish lag_f > lag_o);
+  // kMaxLag bounds them and sizes the record ring.
+  static constexpr int kMaxLag = kTwoShot ? 4 : 1;
   static constexpr int NXB = IN == 0 ? 2 : 0;                        // x row buffers (the residual never sits in shared memory)
-  static constexpr int NREC = (IN == 1 ? 3 : 2) + (kTwoShot ? 1 : 0);
+  static constexpr int NREC = (IN == 1 ? 2 : 1) + kMaxLag;
   static constexpr int kOutBytes = EPI <= 1 ? kRowBytes : (EPI == 2 ? 3584 : 6400);
   static constexpr int kMisc = 128;                                  // mbarriers + reduction scratch
   static constexpr int kTeamBytes = NXB * kRowBytes + kOutBytes + NREC * kRecStride + kMisc;
@@ -138,7 +141,7 @@ struct TeamSync {
 template <int P, int ALGO, int IN, int EPI, int T>
 __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTeams, 1) ar_kernel(const __grid_constant__ ArParams prm) {
   using S = ArShape<P, ALGO, IN, EPI, T>;
-  constexpr int NJ = S::NJ, NXB = S::NXB, NREC = S::NREC, NSG = S::NSG, LAG = S::LAG;
+  constexpr int NJ = S::NJ, NXB = S::NXB, NREC = S::NREC, NSG = S::NSG;
   constexpr bool kTwoShot = S::kTwoShot;
   constexpr int NXB1 = NXB > 0 ? NXB : 1;   // keeps index arithmetic well-formed in shapes without row buffers
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -161,8 +164,8 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   uint8_t* outst = tbase + NXB * kRowBytes;              // output staging row
   uint8_t* recs = outst + S::kOutBytes;                  // NREC encoded records
   uint64_t* xbar = reinterpret_cast<uint64_t*>(recs + NREC * kRecStride);  // [3] x loads
-  uint64_t* qbar = xbar + 2;                             // [4] NVFP4 record loads
-  float* red = reinterpret_cast<float*>(qbar + 4);       // [2][6] reduction exchange
+  uint64_t* qbar = xbar + 2;                             // [6] NVFP4 record loads
+  float* red = reinterpret_cast<float*>(qbar + 6);       // [2][6] reduction exchange
   uint8_t* sentinel = smem + (size_t)nteams * S::kTeamBytes;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sentinel + kRecStride);
   const TeamSync<T> tsync{1 + team};
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   if (threadIdx.x == 0) *abort_flag = 0u;
   if (leader) {
 #pragma unroll
-    for (int i = 0; i < 6; i++) mbar_init(xbar + i, 1);
+    for (int i = 0; i < 8; i++) mbar_init(xbar + i, 1);
   }
   for (int i = threadIdx.x; i < kRecStride / 16; i += blockDim.x) {
     uint4 v;
@@ -370,7 +373,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   auto window_source = [&](int i) { return IN == 2 ? i : i + (i >= me ? 1 : 0); };
 
   // =============================================================================================
-  // main pipeline.  Step k: (two-shot) owner step of row k-1; encode + push row k; finish row k-LAG.
+  // main pipeline.  Step k: (two-shot) owner step of row k-lag_o; encode + push row k; finish row k-lag_f.
   // =============================================================================================
 #ifdef FP4AR_PHASE_TIMERS
   long long phase_t0_ = clock64();
@@ -381,7 +384,9 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     return rowscale_pending(bits) ? poll_rowscale(rec, row, src, phase) : __uint_as_float(bits);
   };
 
-  for (int k = 0; k < nk + LAG; k++) {
+  const int lag_o = kTwoShot ? prm.lag_owner : 0;
+  const int lag_f = kTwoShot ? prm.lag_finish : 1;
+  for (int k = 0; k < nk + lag_f; k++) {
     FP4AR_PHASE(0);
     if (leader) bulk_wait_source_free<0>();
     tsync.sync();
@@ -393,10 +398,10 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     }
 
     // ------------------------------------------------------------------ early window loads
-    // (a) the row finished in this step (k - LAG): one-shot sources, or the owner's broadcast of a row owned by a peer;
+    // (a) the row finished in this step (k - lag_f): one-shot sources, or the owner's broadcast of a row owned by a peer;
     // (b) two-shot: the reduce-scatter sources of row k-1 when this rank owns it.
     // Everything was pushed at least one full step ago; stage-specific code validates and falls back to polling.
-    const int kf = k - LAG;                          // row index (in this team's sequence) finished in this step
+    const int kf = k - lag_f;                        // row index (in this team's sequence) finished in this step
     const bool fin = kf >= 0 && kf < nk;
     const int frow = fin ? row_of(kf) : 0;
     const bool fin_owned = kTwoShot && fin && (frow % P) == me;
@@ -438,11 +443,11 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     }
     FP4AR_PHASE(2);   // early loads issued
 
-    // ------------------------------------------------------------------ owner step of row k-1 (two-shot)
+    // ------------------------------------------------------------------ owner step of row k-lag_o (two-shot)
     // Reduce every source, re-encode into rec, broadcast.  The row is finished (decoded, epilogue) one step later
     // like every other row, from the record kept in the ring.
     if constexpr (kTwoShot) {
-      const int ko = k - 1;
+      const int ko = k - lag_o;
       if (ko >= 0 && ko < nk && (row_of(ko) % P) == me) {
         const int row = row_of(ko);
         uint8_t* rec_own = recs + (ko % NREC) * kRecStride;
@@ -658,7 +663,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     }
     FP4AR_PHASE(6);   // encode pass 2 + push
 
-    // ------------------------------------------------------------------ stage B: finish row k - LAG
+    // ------------------------------------------------------------------ stage B: finish row k - lag_f
     if (fin) {
       const int row = frow;
       uint8_t* rec_own = recs + (kf % NREC) * kRecStride;

@@ -63,10 +63,10 @@ class Cell:
         self.outq = torch.empty(rows, nb, dtype=torch.uint8, device=dev) if epi >= 2 else None
         self.rows, self.kind, self.epi = rows, kind, epi
 
-    def args(self, i, mode, algo, teams, tw, rows=None):
+    def args(self, i, mode, algo, teams, tw, rows=None, lags=0):
         return make_args(x=self.xs[i % self.nsets], out=self.out, rows=self.rows if rows is None else rows, mode=mode,
                          algo=algo, input=self.kind, epilogue=self.epi, gs=self.gs, res_in=self.res, res_out=self.res,
-                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw)
+                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw, lags=lags)
 
 
 def main(argv=None) -> int:
@@ -78,6 +78,7 @@ def main(argv=None) -> int:
     ap.add_argument("--algos", default="auto")
     ap.add_argument("--team-warps", default="0")
     ap.add_argument("--teams", default="0")
+    ap.add_argument("--lags", default="0", help="two-shot depths, comma list of lag_owner+16*lag_finish (e.g. 33 = 1,2; 50 = 2,3; 66 = 2,4)")
     ap.add_argument("--graph", type=int, default=10)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
@@ -120,18 +121,18 @@ def main(argv=None) -> int:
                 cell = Cell(rows, INPUTS[inp], epi, rank, world, dev)
                 for algo in ns.algos.split(","):
                     for tw in (int(t) for t in ns.team_warps.split(",")):
-                        for teams in (int(t) for t in ns.teams.split(",")):
+                        for teams, lags in ((int(t), int(l)) for t in ns.teams.split(",") for l in ns.lags.split(",")):
                             res = {}
                             for mode in ns.modes.split(","):
                                 if mode == "empty":
-                                    fn = lambda i: ctx.launch(cell.args(i, N.MODE_FUSED, ALGOS[algo], teams, tw, rows=0))
+                                    fn = lambda i: ctx.launch(cell.args(i, N.MODE_FUSED, ALGOS[algo], teams, tw, rows=0, lags=lags))
                                 else:
-                                    fn = lambda i, m=MODES[mode]: ctx.launch(cell.args(i, m, ALGOS[algo], teams, tw))
+                                    fn = lambda i, m=MODES[mode]: ctx.launch(cell.args(i, m, ALGOS[algo], teams, tw, lags=lags))
                                 t, c = timed(fn)
                                 res[mode] = t["med_us"]
                                 st = ctx.status()
                                 emit({**common, "variant": "fp4ar", "mode": mode, "algo": algo, "rows": rows,
-                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams,
+                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags,
                                       "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
                                       "p90_us": round(t["p90_us"], 3), "sm_mhz": c.get("sm_mhz"),
                                       "reasons": c.get("reasons"), "status": st.describe(),

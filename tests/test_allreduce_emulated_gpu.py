@@ -90,3 +90,12 @@ def test_modes_run_and_leave_the_window_armed():
             assert sum(mismatches(c, inp, outs, r) for r in range(2)) == 0
     assert g.status(0).ok
     g.close()
+
+
+@pytest.mark.parametrize("P", [4, 8])
+@pytest.mark.parametrize("lags", [33, 49, 50, 66, 67])
+def test_two_shot_pipeline_depths(P, lags):
+    """Every legal (owner lag, finish lag) pair gives the same bits; rows per team range from 0 to several."""
+    for rows, epi in ((700, 0), (37, 1)):
+        rec = gate_cell_emulated(CellConfig(nranks=P, rows=rows, epilogue=epi, lags=lags), reps=4, graph_calls=3, graph_reps=2)
+        assert rec["pass"], (lags, rows, rec)
