@@ -128,6 +128,10 @@ int fp4ar_add_rmsnorm(const void* x_bf16, const void* res_in, void* res_out, con
 /* window = nbuffers buffers of buffer_bytes each; receive slots start at every buffer's first byte */
 int fp4ar_fill_sentinel(void* window, size_t buffer_bytes, int nbuffers, fp4ar_stream stream);
 
+/* Exhaustive check of the encoder's division-free multiplier for one exponent of the row-scale inverse (27..227):
+ * adds the number of (mantissa, scale byte) cases that differ from IEEE division to *device_mismatch_counter. */
+int fp4ar_selftest_scale_division(int exp_biased, unsigned long long* device_mismatch_counter, fp4ar_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -198,6 +198,37 @@ __device__ __forceinline__ uint32_t pair_block_scales(float bm0, float bm1, floa
   return sf2;
 }
 
+// The same with a table in shared memory: lut[b] = {decode(b), rn(1 / decode(b))} for the 128 non-negative E4M3
+// bytes.  The multiplier rn(inv / decode(b)) is obtained without a division from q0 = rn(inv * rc),
+// q1 = fma(fma(-q0, d, inv), rc, q0), which equals the IEEE quotient for every inv in [2^-100, 2^100] and every
+// finite positive d of the table (checked exhaustively on the GPU by the test-suite); `exact_ok` says whether
+// inv is in that range (the caller computes it once per row), otherwise the IEEE division is used.
+struct ScaleLut { const float2* tab; };
+__device__ __forceinline__ void fill_scale_lut(float2* tab, int tid, int nthreads) {
+  for (int b = tid; b < 128; b += nthreads) {
+    const float d = e4m3_unpack2((uint32_t)b).lo;
+    tab[b] = make_float2(d, d > 0.0f ? __frcp_rn(d) : 0.0f);
+  }
+}
+__device__ __forceinline__ bool scale_lut_range_ok(float inv) { return inv >= 0x1p-100f && inv <= 0x1p100f; }
+__device__ __forceinline__ float lut_multiplier(float inv, float2 e, bool exact_ok) {
+  float m;
+  if (exact_ok) {
+    const float q0 = __fmul_rn(inv, e.y);
+    m = __fmaf_rn(__fmaf_rn(-q0, e.x, inv), e.y, q0);
+  } else {
+    m = __fdiv_rn(inv, e.x);
+  }
+  return e.x > 0.0f ? m : 0.0f;
+}
+__device__ __forceinline__ uint32_t pair_block_scales_lut(float bm0, float bm1, float inv, ScaleLut lut, bool exact_ok,
+                                                          float& mult0, float& mult1) {
+  const uint32_t sf2 = e4m3_pack2(div6(__fmul_rn(bm0, inv)), div6(__fmul_rn(bm1, inv)));
+  mult0 = lut_multiplier(inv, lut.tab[sf2 & 0x7fu], exact_ok);
+  mult1 = lut_multiplier(inv, lut.tab[(sf2 >> 8) & 0x7fu], exact_ok);
+  return sf2;
+}
+
 // Eight BF16 (one 16 B chunk) times mult -> E2M1 word.
 template <bool CANON>
 __device__ __forceinline__ uint32_t quant_chunk_bf16(uint4 c, float mult) {
@@ -225,6 +256,28 @@ __device__ __forceinline__ uint32_t encode_pair_f32(const float* f, float inv, u
   for (int i = 0; i < 16; i++) { bm0 = fmaxf(bm0, fabsf(f[i])); bm1 = fmaxf(bm1, fabsf(f[16 + i])); }
   float m0, m1;
   const uint32_t sf2 = pair_block_scales(bm0, bm1, inv, m0, m1);
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const F2 mm = f2_splat(k < 2 ? m0 : m1);
+    F2 g[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { F2 v; v.lo = f[8 * k + 2 * i]; v.hi = f[8 * k + 2 * i + 1]; g[i] = f2_mul(v, mm); }
+    w[k] = e2m1_pack8(g[0], g[1], g[2], g[3]);
+    if (CANON) w[k] = canon_neg0(w[k]);
+  }
+  q = make_uint4(w[0], w[1], w[2], w[3]);
+  return sf2;
+}
+
+// encode_pair_f32 with the table-based multipliers.
+template <bool CANON>
+__device__ __forceinline__ uint32_t encode_pair_f32_lut(const float* f, float inv, ScaleLut lut, bool exact_ok, uint4& q) {
+  float bm0 = 0.0f, bm1 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; i++) { bm0 = fmaxf(bm0, fabsf(f[i])); bm1 = fmaxf(bm1, fabsf(f[16 + i])); }
+  float m0, m1;
+  const uint32_t sf2 = pair_block_scales_lut(bm0, bm1, inv, lut, exact_ok, m0, m1);
   uint32_t w[4];
 #pragma unroll
   for (int k = 0; k < 4; k++) {

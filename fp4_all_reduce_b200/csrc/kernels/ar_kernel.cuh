@@ -74,7 +74,7 @@ struct ArShape {
   static constexpr int kOutBytes = EPI <= 1 ? kRowBytes : (EPI == 2 ? 3584 : 6400);
   static constexpr int kMisc = 128;                                  // mbarriers + reduction scratch
   static constexpr int kTeamBytes = NXB * kRowBytes + kOutBytes + NREC * kRecStride + kMisc;
-  static constexpr int kCtaExtra = kRecStride + 128;                 // sentinel record + abort flag
+  static constexpr int kCtaExtra = kRecStride + 128 + 1024;          // sentinel record + abort flag + scale table
   static constexpr int NSG = IN == 2 ? P : P - 1;                    // sources read from the window
   // Two-shot owners hold a whole FP32 row slice in registers and the norm epilogue holds BF16 z and the
   // residual: those shapes get fewer, fatter threads.
@@ -168,6 +168,8 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   float* red = reinterpret_cast<float*>(qbar + 6);       // [2][6] reduction exchange
   uint8_t* sentinel = smem + (size_t)nteams * S::kTeamBytes;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sentinel + kRecStride);
+  float2* scale_tab = reinterpret_cast<float2*>(sentinel + kRecStride + 128);
+  const ScaleLut slut{scale_tab};
   const TeamSync<T> tsync{1 + team};
 
   // ---- prologue: nothing here touches global memory written by an earlier kernel ----
@@ -184,6 +186,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     else v = make_uint4(0, 0, 0, 0);
     sts16(sentinel + 16 * i, v);
   }
+  fill_scale_lut(scale_tab, threadIdx.x, blockDim.x);
   mbar_init_fence();
   fence_smem_to_async();
   __syncthreads();
@@ -519,12 +522,13 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
         }
         const RowScale sc = row_scale_from_amax(am);
+        const bool lut_ok = scale_lut_range_ok(sc.inv);
         if (!xport) {
 #pragma unroll
           for (int j = 0; j < NJ; j++) {
             const int p = lane + 32 * (tw + T * j);
             uint4 q;
-            uint32_t sf2 = encode_pair_f32<true>(sums[j], sc.inv, q);   // slot order
+            uint32_t sf2 = encode_pair_f32_lut<true>(sums[j], sc.inv, slut, lut_ok, q);   // slot order
             lane_permute4(q.x, q.y, q.z, q.w, f);
             if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
             sts16(rec_own + 16 * p, q);
@@ -596,13 +600,14 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
             for (int g = 0; g < 6; g++) am = fmaxf(am, g6[g]);
           }
           const RowScale sc = row_scale_from_amax(am);
+          const bool lut_ok = scale_lut_range_ok(sc.inv);
           FP4AR_PHASE(5);   // amax pass + exchange
 #pragma unroll
           for (int j = 0; j < NJ; j++) {
             const int p = lane + 32 * (tw + T * j);
             const float bm0 = __uint_as_float(bmp[j] << 16), bm1 = __uint_as_float(bmp[j] & 0xffff0000u);
             float m0, m1;
-            const uint32_t sf2 = pair_block_scales(bm0, bm1, sc.inv, m0, m1);
+            const uint32_t sf2 = pair_block_scales_lut(bm0, bm1, sc.inv, slut, lut_ok, m0, m1);
             const float mlo = (f & 2) ? m1 : m0, mhi = (f & 2) ? m0 : m1;
             uint32_t w0 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((0 ^ f) << 4)), mlo);
             uint32_t w1 = quant_chunk_bf16<true>(lds16(xrow + p * 64 + ((1 ^ f) << 4)), mlo);

@@ -462,6 +462,35 @@ extern "C" int fp4ar_fill_sentinel(void* window, size_t buffer_bytes, int nbuffe
 }
 
 // ---------------------------------------------------------------------------------------------
+// Self-test of the division-free multiplier: for one biased exponent of inv, every mantissa and every positive
+// finite E4M3 byte, count the cases where it differs from the IEEE quotient (must be zero).
+// Reference project counterpart: test T2 of bench/codec/codec_bench.cu:45-64.
+// ---------------------------------------------------------------------------------------------
+namespace fp4ar {
+__global__ void scale_division_selftest_kernel(uint32_t exp_biased, unsigned long long* mismatches) {
+  __shared__ float2 tab[128];
+  fill_scale_lut(tab, threadIdx.x, blockDim.x);
+  __syncthreads();
+  unsigned long long bad = 0;
+  for (uint32_t man = blockIdx.x * blockDim.x + threadIdx.x; man < (1u << 23); man += gridDim.x * blockDim.x) {
+    const float inv = __uint_as_float((exp_biased << 23) | man);
+    for (int b = 1; b < 127; b++) {
+      const float want = __fdiv_rn(inv, tab[b].x);
+      const float got = lut_multiplier(inv, tab[b], true);
+      bad += __float_as_uint(want) != __float_as_uint(got);
+    }
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+}  // namespace fp4ar
+
+extern "C" int fp4ar_selftest_scale_division(int exp_biased, unsigned long long* device_mismatch_counter, fp4ar_stream stream) {
+  if (exp_biased < 27 || exp_biased > 227 || !device_mismatch_counter) return FP4AR_ERR_ARGUMENT;   // 2^-100 .. 2^100
+  fp4ar::scale_division_selftest_kernel<<<1184, 256, 0, (cudaStream_t)stream>>>((uint32_t)exp_biased, device_mismatch_counter);
+  return fp4ar::cuda_check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------
 // fp4ar_reduce_reencode_noalloc (declared and documented in include/fp4ar_noalloc.h): the owner step with
 // its record buffer in a fixed device array instead of caller memory.  No counterpart in the reference.
 // ---------------------------------------------------------------------------------------------

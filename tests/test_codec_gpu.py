@@ -115,3 +115,13 @@ def test_fill_sentinel_pattern():
             r = h[b, slot * 3584:(slot + 1) * 3584]
             assert np.all(r[:3072] == 0x88) and np.all(r[3072:3456] == 0xFF)
             assert np.array_equal(r[3456:3472].view(np.uint32), np.full(4, 0x80000000, np.uint32))
+
+
+def test_division_free_multiplier_is_the_ieee_quotient():
+    """All 2^23 mantissas x 126 scale bytes for exponents across the supported range (about 1e10 cases)."""
+    import ctypes as C
+    cnt = torch.zeros(1, dtype=torch.int64, device=DEV)
+    for e in (27, 28, 64, 100, 126, 127, 128, 150, 200, 226, 227):
+        N.check(N.cuda().fp4ar_selftest_scale_division(e, cnt.data_ptr(), None), "selftest")
+    torch.cuda.synchronize()
+    assert int(cnt.item()) == 0
