@@ -123,7 +123,6 @@ struct fp4ar_ctx {
   StatusWords* status[FP4AR_MAX_RANKS];
   unsigned long long timeout_ns;
   int max_smem_optin;
-  int default_lag_owner, default_lag_finish;
 };
 
 extern "C" size_t fp4ar_window_bytes(int max_rows, int hidden, int nranks) {
@@ -148,7 +147,6 @@ static int create_common(fp4ar_ctx** out, int rank, int nranks, int device, int 
   c->geo = geometry(max_rows, nranks);
   c->window_bytes = window_bytes;
   c->timeout_ns = 2000ull * 1000000ull;
-  c->default_lag_owner = 1; c->default_lag_finish = 2;
   for (int r = 0; r < nranks; r++) c->win[r] = (char*)windows[r];
   int sms = 0;
   FP4AR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -297,14 +295,16 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   prm.flags = (a0.mode == FP4AR_MODE_XPORT ? kFlagXport : 0) | (a0.mode == FP4AR_MODE_COMPUTE ? kFlagLoopback : 0);
   prm.cap = c->geo.cap; prm.capo = c->geo.capo;
   prm.buf_bytes = c->geo.buf_bytes; prm.timeout_ns = c->timeout_ns;
-  // Two-shot pipeline depths: tune[3] = lag_owner | lag_finish << 4 when set; otherwise deep for long row
-  // sequences (ranks decoupled by a full step at each hand-off) and shallow when a team has only a few rows.
+  // Two-shot pipeline depths: tune[3] = lag_owner | lag_finish << 4 when set; otherwise the measured best.  With
+  // eight ranks every row waits on seven peers, so one more step of slack at each hand-off pays at every row count
+  // (16K rows: 284 -> 228 us); with four ranks the kernel is bound by its own codec work at large row counts and the
+  // shallow pipeline (fewest live records per team) wins there, while short sequences gain from the slack.
   {
     int lo = a0.tune[3] & 15, lf = (a0.tune[3] >> 4) & 15;
     if (lo < 1 || lf <= lo || lf > 4) {
-      const int rows_per_team = a0.rows / (c->ctas_per_rank * 4) + 1;
-      lo = 1; lf = 2;
-      if (rows_per_team >= 6) { lo = c->default_lag_owner; lf = c->default_lag_finish; }
+      if (c->nranks >= 6) { lo = 2; lf = 3; }
+      else if (c->nranks >= 3 && a0.rows <= 4096) { lo = 2; lf = 4; }
+      else { lo = 1; lf = 2; }
     }
     prm.lag_owner = lo; prm.lag_finish = lf;
   }
