@@ -7,10 +7,18 @@
   ("bidir": both directions of every link busy, which is what an AllReduce does) and rank 0 alone ("uni");
   methods: bulk store with several chunk sizes, st.v4, bulk load (pull), multimem.st when the fabric offers a
   multicast mapping; CTA counts 16 / 32 / 148.
-* latency: ping-pong between rank 0 and rank 1 through polled slots; one-way = round trip / 2.
+* latency: ping-pong between rank 0 and rank 1; one-way = round trip / 2.  Three hand-offs: the data is the signal
+  (st.volatile into the peer, poll the own memory), payload + st.release.sys flag polled with ld.acquire.sys, and
+  a pull (write the own slot, poll the peer's across the link).
+* publish: tiles written into the peer and published per tile (nothing / fence.acq_rel.sys + flag / st.release.sys
+  flag) -> GB/s versus tile size; and nanoseconds per (remote 16-byte store + fence.acq_rel.sys) from one thread.
+* tear: are 16-byte stores into a peer seen whole?  Rank 0 rewrites 4096 slots of rank 1 with {i,i,i,i} while rank 1
+  polls them; counts loads whose words differ, for 16-byte and (the control) 2 x 8-byte accesses.
+* copy engine: torch `copy_` between the symmetric buffers (cudaMemcpyAsync peer copy) against the SM kernels.
 
 One JSON line per configuration (GB/s of payload per direction per GPU; time = CUDA events, max over ranks).
-The reference's equivalents: bench/micro/bw.cu, lat.cu and their README tables (bench/micro/README.md:48-59).
+The reference's equivalents: bench/micro/bw.cu, lat.cu, fence.cu, tear.cu, bench/link/ce.cu and their README
+tables (bench/micro/README.md:48-59).
 """
 from __future__ import annotations
 
@@ -41,9 +49,14 @@ def main(argv=None) -> int:
     rank, world = dist.get_rank(), dist.get_world_size()
     lib = N.cuda()
     lib.fp4ar_micro_bandwidth.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
-    lib.fp4ar_micro_latency.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.fp4ar_micro_latency.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.fp4ar_micro_copy_engine.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.fp4ar_micro_publish.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.fp4ar_micro_fence_cost.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.fp4ar_micro_tear_writer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.fp4ar_micro_tear_reader.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     total = ns.mb << 20
-    buf, ptrs, handle = allocate_symmetric(total + 4096, dev, dist.group.WORLD)
+    buf, ptrs, handle = allocate_symmetric(total + (1 << 17), dev, dist.group.WORLD)
     mc = multicast_pointer(handle)
     nxt = (rank + 1) % world
     stream = lambda: C.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -85,24 +98,95 @@ def main(argv=None) -> int:
             moved = (total // chunk) * chunk
             emit({"kind": "bw", "method": names[method], "chunk": chunk, "ctas": ctas, "inflight": inflight, "active": active,
                   "tp": world, "mb": ns.mb, "ms": round(ms, 4), "gbs_per_dir": round(moved / ms / 1e6, 1)})
-    # latency between rank 0 and rank 1
-    slots = buf[total:total + 4096]
-    slots.zero_()
-    torch.cuda.synchronize()
-    dist.barrier()
-    out2 = torch.zeros(2, dtype=torch.int64, device=dev)
-    iters = 2000
-    if rank < 2:
-        my_slot = ptrs[rank] + total
-        peer_slot = ptrs[1 - rank] + total      # each rank polls a slot in its own buffer and writes the peer's
-        N.check(lib.fp4ar_micro_latency(my_slot, peer_slot, iters, 1 if rank == 0 else 0, 2000, out2.data_ptr(), stream()),
-                "micro_latency")
-    torch.cuda.synchronize()
-    dist.barrier()
+    def timed(launch, active):
+        """min over iterations of the CUDA-event time of `launch`, max over ranks."""
+        times = []
+        for it in range(ns.iters + 2):
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            if active == "bidir" or rank == 0:
+                launch()
+            b.record()
+            b.synchronize()
+            if it >= 2:
+                times.append(a.elapsed_time(b))
+        t = torch.tensor([min(times)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # copy engine: a peer copy issued by the runtime (cudaMemcpyAsync) instead of an SM kernel
+    src = torch.empty(total, dtype=torch.uint8, device=dev)
+    for active in ("bidir", "uni"):
+        for name, d, s_ in (("copy_engine_push", ptrs[nxt], src.data_ptr()), ("copy_engine_pull", src.data_ptr(), ptrs[nxt])):
+            ms = timed(lambda: N.check(lib.fp4ar_micro_copy_engine(d, s_, total, stream()), "copy_engine"), active)
+            emit({"kind": "bw", "method": name, "chunk": total, "ctas": 0, "inflight": 1, "active": active,
+                  "tp": world, "mb": ns.mb, "ms": round(ms, 4), "gbs_per_dir": round(total / ms / 1e6, 1)})
+    del src
+
+    # publication cost per tile
+    flags_off = total
+    for tile in (1024, 4096, 16384, 65536):
+        base = None
+        for mode, mname in ((0, "none"), (1, "fence_acq_rel_sys+flag"), (2, "st_release_sys_flag")):
+            ms = timed(lambda: N.check(lib.fp4ar_micro_publish(ptrs[nxt], ptrs[nxt] + flags_off, total, tile, mode, 148,
+                                                               stream()), "micro_publish"), "bidir")
+            base = ms if mode == 0 else base
+            emit({"kind": "publish", "publish": mname, "tile": tile, "ctas": 148, "tp": world, "ms": round(ms, 4),
+                  "gbs_per_dir": round(total / ms / 1e6, 1), "vs_unpublished": round(ms / base, 3)})
+    out1 = torch.zeros(1, dtype=torch.int64, device=dev)
+    fence_ns = {}
+    for wf in (0, 1):
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            N.check(lib.fp4ar_micro_fence_cost(ptrs[nxt], 4000, wf, out1.data_ptr(), stream()), "micro_fence_cost")
+            torch.cuda.synchronize()
+            fence_ns[wf] = int(out1.item()) / 4000
     if rank == 0:
-        ns_total, gave_up = int(out2[0].item()), int(out2[1].item())
-        emit({"kind": "latency", "method": "polled_slot_st_volatile", "iters": iters, "one_way_us": round(ns_total / iters / 2 / 1e3, 3),
-              "gave_up": gave_up})
+        emit({"kind": "fence", "ns_per_remote_store": round(fence_ns[0], 1),
+              "ns_per_remote_store_plus_fence_acq_rel_sys": round(fence_ns[1], 1)})
+
+    # latency between rank 0 and rank 1
+    slots = buf[total:total + (1 << 17)]
+    iters = 2000
+    out3 = torch.zeros(3, dtype=torch.int64, device=dev)
+    for method, mname in ((0, "data_is_signal_st_volatile"), (1, "payload+st_release_sys_flag"), (2, "pull_poll_peer")):
+        slots.zero_()
+        out3.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank < 2:
+            my_slot = ptrs[rank] + total
+            peer_slot = ptrs[1 - rank] + total
+            N.check(lib.fp4ar_micro_latency(my_slot, peer_slot, iters, 1 if rank == 0 else 0, method, 1000, out3.data_ptr(),
+                                            stream()), "micro_latency")
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            ns_total, gave_up = int(out3[0].item()), int(out3[1].item())
+            emit({"kind": "latency", "method": mname, "iters": iters, "one_way_us": round(ns_total / iters / 2 / 1e3, 3),
+                  "gave_up": gave_up})
+
+    # tear: rank 0 writes into rank 1, rank 1 polls its own memory; neither waits for the other
+    nslots = 4096
+    out2 = torch.zeros(2, dtype=torch.int64, device=dev)
+    for how, hname in ((0, "16B_store_16B_load"), (1, "2x8B_store_2x8B_load")):
+        slots.zero_()
+        out2.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            N.check(lib.fp4ar_micro_tear_writer(ptrs[1] + total, nslots, 3000, how, stream()), "tear_writer")
+        elif rank == 1:
+            N.check(lib.fp4ar_micro_tear_reader(ptrs[1] + total, nslots, 3000, how, out2.data_ptr(), stream()), "tear_reader")
+        torch.cuda.synchronize()
+        res = out2.clone()
+        dist.broadcast(res, src=1)
+        if rank == 0:
+            emit({"kind": "tear", "access": hname, "slots": nslots, "polls_per_slot": 3000, "torn_loads": int(res[0].item()),
+                  "value_changes_seen": int(res[1].item())})
     if rank == 0 and ns.out:
         with open(ns.out, "a") as f:
             for r in records:
