@@ -42,9 +42,9 @@ from dataclasses import dataclass, field
 from typing import Callable, Optional
 
 HARNESS_MODULES = ("bench_cli", "gate_dist", "gemm_ar_bench", "micro", "ops_bench", "gemm_bench", "nccl_tuned",
-                   "profile_case", "block_bench", "pull_bench")
+                   "profile_case", "block_bench", "compare_bench")
 TAKES_OUT_TAG = ("bench_cli",)
-TAKES_OUT = ("bench_cli", "gate_dist", "gemm_ar_bench", "micro", "nccl_tuned", "block_bench", "pull_bench")
+TAKES_OUT = ("bench_cli", "gate_dist", "gemm_ar_bench", "micro", "nccl_tuned", "block_bench", "compare_bench")
 SELF_LAUNCHING = ("nccl_tuned",)      # start their own ranks: never wrapped in torch.distributed.run
 BAD_REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")
 
