@@ -57,12 +57,17 @@ def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int
 
     rec = {"kind": "check", "tp": world, "rows": cfg.rows, "hidden": N.HIDDEN, "algo": cfg.resolved_algo(),
            "input": cfg.input, "epilogue": cfg.epilogue, "dist": cfg.dist, "negctl": negctl}
+    # Building the inputs runs the host model, whose duration differs between the rank processes (they share the
+    # CPU cores); the device-side waits are bounded, so the ranks are lined up before the first launch.
+    torch.cuda.synchronize()
+    dist.barrier()
     # 1: first call
     call(0)
     rec["mism_first"] = total(compare(0))
     st = ctx.status()
     if total(st.code) != 0:
         rec["status"] = st.describe()
+        rec["ranks_with_error"] = total(int(st.code != 0))
         rec["pass"] = False
         return rec
     if cfg.epilogue == N.EPI_NONE:
@@ -175,7 +180,10 @@ def main(argv=None) -> int:
                     records.append(rec)
                     if rank == 0:
                         print(json.dumps(rec), flush=True)
-                    if not rec["pass"] and "did not arrive" in str(rec.get("status", "")):
+                    # a wait that gave up on ANY rank leaves slots un-armed: re-arm everywhere (collective decision)
+                    code = torch.tensor([int(ctx.status().code != 0)], dtype=torch.int64, device=dev)
+                    dist.all_reduce(code)
+                    if int(code.item()) != 0:
                         ctx.reset()
     if rank == 0 and ns.out:
         with open(ns.out, "a") as f:

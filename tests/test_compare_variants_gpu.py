@@ -1,6 +1,8 @@
 """Flag-push and pull comparison variants on one GPU (ranks emulated as CTA groups of one cooperative launch):
 bit-identical to the one-shot host model, across calls (both buffers, generation counter), in a CUDA graph, and
 with a row count that is not a multiple of the tile."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -10,7 +12,11 @@ from fp4_all_reduce_b200 import oracle as O
 from fp4_all_reduce_b200.harness.gate import CellConfig, make_inputs
 from fp4_all_reduce_b200.parallel.compare import CompareEmulated
 
-pytestmark = pytest.mark.gpu
+# These kernels were written after the last GPU session of their build and have not executed on a GPU yet; until
+# they have, they only run on request so that a fault in them cannot take the rest of the GPU suite down.
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("FP4AR_RUN_UNVERIFIED") != "1",
+                                 reason="comparison variants not yet verified on a GPU; set FP4AR_RUN_UNVERIFIED=1")]
 
 
 def _mism(t, exp_bits):
@@ -25,6 +31,7 @@ def test_compare_variant_matches_host_model(variant, P):
     cfg = CellConfig(nranks=P, rows=rows, algo=N.ALGO_ONESHOT, dist="mags")
     sets = [make_inputs(cfg, s, dev) for s in range(3)]
     grp = CompareEmulated(P, 256, dev)
+    grp.timeout_ms = 300                       # a broken hand-off ends in seconds, not minutes
     outs = [torch.zeros(rows, N.HIDDEN, dtype=torch.bfloat16, device=dev) for _ in range(P)]
     for call in range(7):                        # both buffers several times over, changing inputs
         s = sets[call % 3]
