@@ -31,6 +31,15 @@ PUBLISHED_AR_US = {2: {1024: 10.8, 2048: 15.2, 4096: 21.9, 8192: 34.4, 16384: 60
                    4: {1024: 19.8, 2048: 25.6, 4096: 34.8, 8192: 56.2, 16384: 103.8}}
 
 
+def _claim_stdout():
+    """Keep stdout for the one JSON line: everything else that writes to file descriptor 1 from here on (library
+    banners such as NCCL's version line included) goes to stderr.  Returns the stream to print the result to."""
+    sys.stdout.flush()
+    result = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return result
+
+
 def reference_arm(ns) -> int:
     """The reference's own fused block kernel (kernels/fused_norm/lnorm.cu, untouched, built by
     baseline/build_ref.py) timed with the same protocol: a graph of 121 blocks, device-timed, max over ranks.
@@ -39,6 +48,7 @@ def reference_arm(ns) -> int:
     other torchrun ranks only wait."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
+    result_out = _claim_stdout()
     rec = None
     if rank == 0:
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -65,7 +75,7 @@ def reference_arm(ns) -> int:
                            "p10_us": r["p10_us"], "p90_us": r["p90_us"]}
         except Exception as e:  # the arm must never take the benchmark down
             rec = {"impl": "reference", "unavailable": f"driver failed: {type(e).__name__}: {str(e)[:200]}"}
-        print(json.dumps(rec), flush=True)
+        print(json.dumps(rec), file=result_out, flush=True)
     return 0
 
 
@@ -82,6 +92,7 @@ def main() -> int:
     if ns.impl == "reference":
         return reference_arm(ns)
     ns.warmup = max(ns.warmup, 3)
+    result_out = _claim_stdout()
 
     import torch
     import torch.distributed as dist
@@ -194,7 +205,7 @@ def main() -> int:
         "sweep": sweep, "nccl_us": nccl_us,
     }
     if rank == 0:
-        print(json.dumps(rec))
+        print(json.dumps(rec), file=result_out, flush=True)
     ctx.close()
     if world > 1:
         dist.barrier()
