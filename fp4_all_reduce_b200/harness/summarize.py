@@ -46,11 +46,12 @@ def timing_tables(recs, ceiling):
         if str(r.get("variant", "")).startswith("nccl"):
             nccl[(r["tp"], r["rows"], r["epilogue"])] = r["med_us"]
             continue
-        key = (r["tp"], r["input"], r["epilogue"], r.get("algo", "auto"), r.get("team_warps", 0), r["rows"])
+        key = (r["tp"], r.get("variant", "fp4ar"), r["input"], r["epilogue"], r.get("algo", "auto"), r.get("team_warps", 0),
+               r.get("lags", 0), r["rows"])
         cells[key][r["mode"]] = r
     rows = []
-    for key in sorted(cells, key=lambda k: (k[0], k[1], k[2], str(k[3]), k[4], k[5])):
-        tp, inp, epi, algo, tw, nrows = key
+    for key in sorted(cells, key=lambda k: (k[0], k[1], k[2], k[3], str(k[4]), k[5], k[6], k[7])):
+        tp, variant, inp, epi, algo, tw, lags, nrows = key
         c = cells[key]
         F = c.get("fused", {}).get("med_us")
         X = c.get("xport", {}).get("med_us")
@@ -59,22 +60,50 @@ def timing_tables(recs, ceiling):
         ov = None
         if None not in (F, X, Cc, E) and min(X - E, Cc - E) > 0:
             ov = round((X + Cc - F - E) / min(X - E, Cc - E), 2)
-        base = nccl.get((tp, nrows, epi)) if inp == "bf16" else nccl.get((tp, nrows, epi))
+        base = nccl.get((tp, nrows, epi))    # the BF16 NCCL baseline is the comparison point of both input kinds
         wire = c.get("fused", {}).get("wire_gbs")
         frac = round(wire / ceiling, 2) if wire and ceiling else None
-        rows.append([tp, inp, epi, nrows, F, X, Cc, E, ov, base, round(base / F, 2) if base and F else None, wire, frac])
+        tune = ("T%d " % tw if tw else "") + ("lags %d,%d" % (lags & 15, lags >> 4) if lags else "")
+        rows.append([tp, variant, tune.strip(), inp, epi, nrows, F, X, Cc, E, ov, base,
+                     round(base / F, 2) if base and F else None, wire, frac])
     if not rows:
         return ""
-    return table(["TP", "input", "epilogue", "rows", "fused us", "xport us", "compute us", "empty us", "corr. overlap",
+    return table(["TP", "variant", "tune", "input", "epilogue", "rows", "fused us", "xport us", "compute us", "empty us", "corr. overlap",
                   "NCCL BF16 (+norm) us", "speed-up", "wire GB/s", "of push ceiling"], rows)
+
+
+def verdict(recs, expect_fail: bool = False) -> tuple[int, str]:
+    """Exit code and one line for a set of gate records: green when there is at least one cell and every cell
+    passed; with expect_fail (negative controls) green when every cell FAILED with mismatches.  The reference
+    project's counterpart is tests/gate_check.py:31-79."""
+    checks = [r for r in recs if r.get("kind") == "check" and "pass" in r]
+    if not checks:
+        return 3, "GATE RED: no check records"
+    if expect_fail:
+        undetected = [r for r in checks if r["pass"] or not (r.get("mism_first", 0) or r.get("bad_calls_percall", 0))]
+        if undetected:
+            return 3, f"NEGATIVE CONTROL RED: {len(undetected)} of {len(checks)} corrupted cells were not detected"
+        return 0, f"NEGATIVE CONTROL GREEN: all {len(checks)} corrupted cells were detected"
+    bad = [r for r in checks if not r["pass"]]
+    if bad:
+        first = bad[0]
+        where = {k: first.get(k) for k in ("tp", "rows", "input", "epilogue", "algo", "variant") if k in first}
+        return 3, f"GATE RED: {len(bad)} of {len(checks)} cells failed, first {where}: {first.get('status', '')}"
+    return 0, f"GATE GREEN: {len(checks)} cells"
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("files", nargs="+")
+    ap.add_argument("--verdict", action="store_true", help="print the gate verdict and exit 3 when it is red")
+    ap.add_argument("--expect-fail", action="store_true", help="with --verdict: the records are negative controls")
     ap.add_argument("--ceiling", type=float, default=None, help="bulk-store payload ceiling in GB/s (default: from a micro record)")
     ns = ap.parse_args(argv)
     recs = load(ns.files)
+    if ns.verdict:
+        code, line = verdict(recs, ns.expect_fail)
+        print(line)
+        return code
     ceiling = ns.ceiling
     bw = [r for r in recs if r.get("kind") == "bw"]
     if ceiling is None and bw:
@@ -83,7 +112,7 @@ def main(argv=None) -> int:
     if t:
         print("### Fused AllReduce timing (graph, per call, max over ranks)\n")
         print(t + "\n")
-    checks = [r for r in recs if r.get("kind") == "check" and "rows" in r]
+    checks = [r for r in recs if r.get("kind") == "check" and "rows" in r and "input" in r]
     if checks:
         print("### Gate\n")
         print(table(["TP", "rows", "input", "epilogue", "algo", "pass", "mism first", "b2b", "bad per-call", "bad graph",
@@ -98,6 +127,20 @@ def main(argv=None) -> int:
     for r in recs:
         if r.get("kind") == "latency":
             print(f"One-way hand-off latency ({r['method']}): {r['one_way_us']} us\n")
+    pub = [r for r in recs if r.get("kind") == "publish"]
+    if pub:
+        print("### Publication cost per tile (st.v4 into the peer, 148 CTAs, both directions busy)\n")
+        print(table(["tile B", "publication", "GB/s", "time vs unpublished"],
+                    [[r["tile"], r["publish"], r["gbs_per_dir"], r["vs_unpublished"]] for r in pub]) + "\n")
+    for r in recs:
+        if r.get("kind") == "fence":
+            print(f"Remote 16-byte store: {r['ns_per_remote_store']} ns; store + fence.acq_rel.sys: "
+                  f"{r['ns_per_remote_store_plus_fence_acq_rel_sys']} ns (one thread, idle link)\n")
+    tear = [r for r in recs if r.get("kind") == "tear"]
+    if tear:
+        print("### 16-byte atomicity over NVLink\n")
+        print(table(["access", "loads", "torn", "value changes seen"],
+                    [[r["access"], r["slots"] * r["polls_per_slot"], r["torn_loads"], r["value_changes_seen"]] for r in tear]) + "\n")
     g = [r for r in recs if r.get("kind") == "timing" and "M" in r]
     if g:
         print("### Row-parallel linear + AllReduce + residual + RMSNorm\n")
