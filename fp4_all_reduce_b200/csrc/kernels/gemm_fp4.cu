@@ -8,7 +8,7 @@
 //                 where the AllReduce kernel in "pushed input" mode finds them, and/or
 //               - into a local [M, N/2 + N/16] NVFP4 tensor.
 //
-// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.
+// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles (128 x 128 selectable), K in blocks of 64.
 //   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
 //                              128-byte swizzle, completion on mbarriers
 //   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
@@ -34,15 +34,27 @@
 
 namespace fp4ar {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kABytes = kBM * kBK * 2;            // 16 KB
-constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
-constexpr int kPieceBytes = kBN / 2 + kBN / 16;   // 144 B of one row of one tile: 128 value bytes + 16 scale bytes
-constexpr int kEpiBytes = kBM * kPieceBytes;      // 18 KB staging
 constexpr int kGemmThreads = 192;
-constexpr int kGemmSmem = kStages * kStageBytes + kEpiBytes + 256 + 1024;   // + barriers + alignment slack
 constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxStages = 6;
+
+// Tile width BN: 256 (4-stage ring) is the large-M shape; 128 (6-stage ring) doubles the number of tiles for small M,
+// where 128 x 256 tiles leave the last wave of the 148 persistent CTAs mostly empty.
+template <int BN>
+struct GemmShape {
+  static_assert(BN == 128 || BN == 256, "tile width");
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kBBytes = BN * kBK * 2;                  // 32 KB / 16 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 32 KB
+  static constexpr int kValueB = BN / 2, kScaleB = BN / 16;     // 128 + 16 B / 64 + 8 B of one row of one tile
+  static constexpr int kPieceBytes = (kValueB + kScaleB + 15) & ~15;   // 144 / 80: keeps every piece 16-byte aligned
+  static constexpr int kEpiBytes = kBM * kPieceBytes;
+  static constexpr int kSmem = kStages * kStageBytes + kEpiBytes + 256 + 1024;   // + barriers + alignment slack
+  // Instruction descriptor: D = F32, A = B = BF16, both K-major, N = BN, M = 128.
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+};
 
 struct GemmParams {
   int M, N, K;
@@ -110,19 +122,18 @@ __device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile) {
   d |= (uint64_t)2 << 61;            // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: D = F32, A = B = BF16, both K-major, N = 256, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 
 // Tile order: the N tiles are walked in panels of kPanel; inside a panel consecutive tile indices step through
 // N fastest and then M.  The ~148 tiles in flight at a time then cover about 18 row blocks x 8 column tiles, which
 // needs (18 + 2*8) * 128 * K * 2 bytes of operands from L2 instead of (6 + 2*24) for a plain row-major walk.
 constexpr int kPanel = 8;
+template <int BN>
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m0, int& n0) {
   const int per_panel = m_tiles * kPanel;
   const int panel = t / per_panel, within = t - panel * per_panel;
   const int width = min(kPanel, n_tiles - panel * kPanel);
   const int m = within / width, n = panel * kPanel + within % width;
-  m0 = m * kBM; n0 = n * kBN;
+  m0 = m * kBM; n0 = n * BN;
 }
 
 struct GemmWait {
@@ -149,22 +160,26 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, const 
   return true;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ GemmParams p) {
+  using S = GemmShape<BN>;
+  constexpr int kStages = S::kStages, kStageBytes = S::kStageBytes, kEpiBytes = S::kEpiBytes, kPieceBytes = S::kPieceBytes;
+  constexpr uint32_t kIdesc = S::kIdesc;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* ring = smem;
   uint8_t* epi = smem + kStages * kStageBytes;
-  uint64_t* full = reinterpret_cast<uint64_t*>(epi + kEpiBytes);   // [kStages]
-  uint64_t* empty = full + kStages;                                 // [kStages]
-  uint64_t* acc_full = empty + kStages;                             // [2]
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi + kEpiBytes);   // [kMaxStages]
+  uint64_t* empty = full + kMaxStages;                              // [kMaxStages]
+  uint64_t* acc_full = empty + kMaxStages;                          // [2]
   uint64_t* acc_empty = acc_full + 2;                               // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = p.N / kBN, m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = p.N / BN, m_tiles = (p.M + kBM - 1) / kBM;
   const int tiles = n_tiles * m_tiles, kblocks = p.K / kBK;
 
   if (threadIdx.x == 0) {
@@ -189,7 +204,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t it = 0;
       for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
         int m0, n0;
-        tile_coords(t, m_tiles, n_tiles, m0, n0);
+        tile_coords<BN>(t, m_tiles, n_tiles, m0, n0);
         for (int kb = 0; kb < kblocks; kb++, it++) {
           const int s = it % kStages;
           if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
@@ -215,7 +230,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t a = tile_i & 1u;
         if (!gemm_wait(acc_empty + a, ((tile_i >> 1) & 1u) ^ 1u, gw, 2)) goto done;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + a * kBN;
+        const uint32_t d_tmem = tmem_base + a * BN;
         for (int kb = 0; kb < kblocks; kb++, it++) {
           const int s = it % kStages;
           if (!gemm_wait(full + s, (it / kStages) & 1u, gw, 3)) goto done;
@@ -240,7 +255,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t tile_i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
       int m0, n0;
-      tile_coords(t, m_tiles, n_tiles, m0, n0);
+      tile_coords<BN>(t, m_tiles, n_tiles, m0, n0);
       const uint32_t a = tile_i & 1u;
       const int row = m0 + r_in_tile;
       // warp-uniform verdict: the tcgen05.ld below is a warp-wide instruction
@@ -248,9 +263,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       tc_fence_after();
       bulk_wait_source_free<0>();   // this thread's previous pieces have left its staging row
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; c++) {
+      for (int c = 0; c < BN / 32; c++) {
         float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * kBN + c * 32, v);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + c * 32, v);
         if (p.dbg_acc && row < p.M) {
           float4* dst = reinterpret_cast<float4*>(p.dbg_acc + (size_t)row * p.N + n0 + c * 32);
 #pragma unroll
@@ -259,29 +274,29 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         uint4 qv;
         const uint32_t sf2 = encode_pair_f32<true>(v, p.inv_gs, qv);
         *reinterpret_cast<uint4*>(my_piece + 16 * c) = qv;
-        *reinterpret_cast<uint16_t*>(my_piece + kBN / 2 + 2 * c) = (uint16_t)sf2;
+        *reinterpret_cast<uint16_t*>(my_piece + S::kValueB + 2 * c) = (uint16_t)sf2;
       }
       tc_fence_before();
       mbar_arrive(acc_empty + a);                 // 128 arrivals hand the accumulator back to the MMA warp
       fence_smem_to_async();
       if (row < p.M) {
         const size_t voff = (size_t)(n0 / 2), soff = (size_t)(p.N / 2 + n0 / 16);
-        if (p.local_q) {
-          char* dst = p.local_q + (size_t)row * qrow_bytes;
-          bulk_store(dst + voff, my_piece, kBN / 2);
-          bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
-        }
+        // one row piece to one destination row: values by a bulk store; scales by a bulk store when they fill a
+        // 16-byte granule (BN = 256), else by one 8-byte store from registers (a bulk copy moves multiples of 16 B)
+        auto put = [&](char* dst) {
+          bulk_store(dst + voff, my_piece, S::kValueB);
+          if constexpr (S::kScaleB == 16) {
+            bulk_store(dst + soff, my_piece + S::kValueB, 16);
+          } else {
+            *reinterpret_cast<uint2*>(dst + soff) = *reinterpret_cast<const uint2*>(my_piece + S::kValueB);
+          }
+        };
+        if (p.local_q) put(p.local_q + (size_t)row * qrow_bytes);
         if (p.nranks) {
           if (p.two_shot) {
-            char* dst = p.win[row % p.nranks] + buf_off + ((size_t)p.rank * p.capo + row / p.nranks) * kRecStride;
-            bulk_store(dst + voff, my_piece, kBN / 2);
-            bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
+            put(p.win[row % p.nranks] + buf_off + ((size_t)p.rank * p.capo + row / p.nranks) * kRecStride);
           } else {
-            for (int d = 0; d < p.nranks; d++) {
-              char* dst = p.win[d] + buf_off + ((size_t)p.rank * p.cap + row) * kRecStride;
-              bulk_store(dst + voff, my_piece, kBN / 2);
-              bulk_store(dst + soff, my_piece + kBN / 2, kBN / 16);
-            }
+            for (int d = 0; d < p.nranks; d++) put(p.win[d] + buf_off + ((size_t)p.rank * p.cap + row) * kRecStride);
           }
         }
       }
@@ -338,9 +353,30 @@ static StatusWords* gemm_status_word() {
 
 using namespace fp4ar;
 
+// 0 = automatic (currently always 256), 128 or 256 = forced.  The 128-wide shape is selectable but not the default
+// until it has been timed against the 256-wide one on the target machine.
+static int g_gemm_tile_n = 0;
+extern "C" int fp4ar_gemm_set_tile_n(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return FP4AR_ERR_ARGUMENT;
+  g_gemm_tile_n = bn;
+  return FP4AR_OK;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  if (cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmem) != cudaSuccess) return cuda_fail();
+  const int tiles = (p.N / BN) * ((p.M + kBM - 1) / kBM);
+  const int sms = device_sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_nvfp4_kernel<BN><<<grid, kGemmThreads, S::kSmem, stream>>>(ma, mb, p);
+  return cuda_check_launch();
+}
+
 extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, const void* wt, int M, int N,
                                 int K, float gs, void* local_q, float* dbg_acc, fp4ar_stream stream) {
-  if (!x || !wt || M < 1 || N < kBN || K < kBK || (N % kBN) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
+  const int bn = g_gemm_tile_n == 128 ? 128 : 256;
+  if (!x || !wt || M < 1 || N < bn || K < kBK || (N % bn) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
   if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
   GemmParams p;
@@ -365,13 +401,8 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   if (!p.status) return cuda_fail();
   p.timeout_ns = 2000000000ull;
   CUtensorMap ma, mb;
-  if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, kBN)) return FP4AR_ERR_UNSUPPORTED;
-  if (cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess) return cuda_fail();
-  const int tiles = (N / kBN) * ((M + kBM - 1) / kBM);
-  const int sms = device_sm_count();
-  const int grid = tiles < sms ? tiles : sms;
-  gemm_nvfp4_kernel<<<grid, kGemmThreads, kGemmSmem, (cudaStream_t)stream>>>(ma, mb, p);
-  return cuda_check_launch();
+  if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, bn)) return FP4AR_ERR_UNSUPPORTED;
+  return bn == 128 ? launch_gemm<128>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256>(ma, mb, p, (cudaStream_t)stream);
 }
 
 extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {
