@@ -379,6 +379,8 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   if (!x || !wt || M < 1 || N < bn || K < kBK || (N % bn) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
   if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
+  // rows of the local NVFP4 tensor are 9N/16 bytes apart and are written with 16-byte bulk stores
+  if (local_q && (N % 256)) return FP4AR_ERR_ARGUMENT;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.inv_gs = 1.0f / gs;
