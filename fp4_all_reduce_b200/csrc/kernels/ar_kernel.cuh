@@ -9,9 +9,10 @@
 // What the reference project does for the same job, for comparison: kernels/push/tp2_l2.cu:744-950
 // (TP2 one-shot), kernels/push/tp4_l4.cu:285-676 (TP4 two-shot), kernels/fused_norm/lnorm.cu:566-697
 // (TP2 + norm).  This kernel is organised differently:
-//   * A team of T warps owns one row at a time and walks its rows as a two-stage software pipeline:
-//     step k encodes and pushes row k, then finishes row k-1 (whose peer data had a whole step to
-//     arrive).  All ranks walk the same rows in the same order, so the waits cannot form a cycle.
+//   * A team of T warps walks its rows as a software pipeline: step k runs (two-shot) the owner step
+//     of row k - lag_owner, encodes and pushes row k, and finishes row k - lag_finish, so that peer data
+//     has whole steps to arrive before it is needed (one-shot: lag_finish = 1).  All ranks walk the
+//     same rows in the same order, so the waits cannot form a cycle.
 //   * A receive slot is re-armed (overwritten with sentinels) by the team that consumed it, in the same
 //     call, while the line is still in L2.  At every call boundary the whole window is sentinel again,
 //     so two buffers (call parity) suffice, one-shot and two-shot share the same memory, and there is
@@ -20,8 +21,9 @@
 //     (slot k holds chunk k ^ ((lane >> 1) & 3)), so that every 64-byte-per-lane shared-memory access
 //     is bank-conflict free with static register indices; only the compact 16 B of E2M1 per pair is
 //     permuted, with 8 selects.
-//   * Rows move between global and shared memory with bulk asynchronous copies only; outputs leave
-//     through a 12 KB staging row and one bulk store.
+//   * Input rows enter shared memory by bulk asynchronous copies; outputs and records leave through
+//     staging rows and one bulk store each.  The residual row of the norm epilogue goes global ->
+//     registers -> global (every lane owns whole 64-byte pieces).
 //   * Every wait is bounded (see fp4ar_async.cuh).
 #pragma once
 #include "../include/fp4ar_codec.cuh"
@@ -402,7 +404,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
 
     // ------------------------------------------------------------------ early window loads
     // (a) the row finished in this step (k - lag_f): one-shot sources, or the owner's broadcast of a row owned by a peer;
-    // (b) two-shot: the reduce-scatter sources of row k-1 when this rank owns it.
+    // (b) two-shot: the reduce-scatter sources of row k - lag_owner when this rank owns it (loaded in the owner step).
     // Everything was pushed at least one full step ago; stage-specific code validates and falls back to polling.
     const int kf = k - lag_f;                        // row index (in this team's sequence) finished in this step
     const bool fin = kf >= 0 && kf < nk;
@@ -447,8 +449,8 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     FP4AR_PHASE(2);   // early loads issued
 
     // ------------------------------------------------------------------ owner step of row k-lag_o (two-shot)
-    // Reduce every source, re-encode into rec, broadcast.  The row is finished (decoded, epilogue) one step later
-    // like every other row, from the record kept in the ring.
+    // Reduce every source, re-encode into rec, broadcast.  The row is finished (decoded, epilogue) lag_finish -
+    // lag_owner steps later like every other row, from the record kept in the ring.
     if constexpr (kTwoShot) {
       const int ko = k - lag_o;
       if (ko >= 0 && ko < nk && (row_of(ko) % P) == me) {
@@ -729,7 +731,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           auto extra = [&]() {};
           finish_row(row, fill, extra);
         } else {
-          // ---- two-shot, row owned by a peer: its broadcast arrived during the previous step ----
+          // ---- two-shot, row owned by a peer: its broadcast had lag_finish - lag_owner steps to arrive ----
           const char* src = fsrc[0];
           const int owner = row % P;
           const float rs = f_has_rs ? settle_rs(frs[0], src, row, owner, 3) : prm.gs[me];
