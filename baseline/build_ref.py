@@ -11,7 +11,6 @@ The reference's harness itself cannot be linked here: it needs ncclGetLsaDeviceP
 from __future__ import annotations
 
 import argparse
-import os
 import shutil
 import subprocess
 import sys

@@ -20,14 +20,13 @@ and tests/negative_control.sh:11-18) re-stated for one-process-per-GPU groups an
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Optional, Sequence
+from typing import Optional
 
 import numpy as np
 import torch
 
 from .. import _native as N
 from .. import oracle as O
-from ..ops import codec
 from ..parallel.context import EmulatedGroup, make_args
 from ..utils import data as D
 

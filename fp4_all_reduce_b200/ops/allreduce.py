@@ -15,7 +15,7 @@ This is the op surface the reference project only plans (docs/INTEGRATION.md:18-
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict
 
 import torch
 

@@ -5,7 +5,6 @@ Counterpart of the reference project's integration gate (harness/fp4ar_bench.cu:
 tests/negative_control.sh), which needs 2 or 4 GPUs; the multi-GPU form of this gate is
 tests/test_allreduce_multigpu.py.
 """
-import numpy as np
 import pytest
 import torch
 

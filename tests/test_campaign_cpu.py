@@ -1,7 +1,6 @@
 """Campaign driver and clock control, on the host only: cells are tiny python children, NVML is a fake."""
 import json
 import os
-import sys
 
 import pytest
 

@@ -8,7 +8,6 @@ symbol twice in a row and requires the BF16 output to equal, bit for bit, what t
 built-in capacity is refused with a message.  The file is named so that pytest collects it last."""
 import ctypes as C
 
-import numpy as np
 import pytest
 import torch
 
