@@ -203,6 +203,11 @@ def main() -> int:
         "status": status.describe(),
         "sweep": sweep, "nccl_us": nccl_us,
     }
+    try:
+        from fp4_all_reduce_b200.utils.runinfo import run_info
+        rec["run"] = run_info(dev)
+    except Exception:      # provenance fields are optional: never lose the measurement over them
+        pass
     if rank == 0:
         print(json.dumps(rec), file=result_out, flush=True)
     ctx.close()

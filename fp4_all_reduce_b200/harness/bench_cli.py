@@ -20,7 +20,6 @@ import argparse
 import json
 import os
 import sys
-import time
 
 import torch
 import torch.distributed as dist
@@ -32,6 +31,7 @@ from ..parallel.context import Fp4ArContext, make_args
 from ..utils import data as D
 from ..utils import timing
 from ..utils.clocks import ClockSampler
+from ..utils.runinfo import run_info
 
 MODES = {"fused": N.MODE_FUSED, "xport": N.MODE_XPORT, "compute": N.MODE_COMPUTE}
 INPUTS = {"bf16": N.IN_BF16, "nvfp4": N.IN_NVFP4}
@@ -98,8 +98,7 @@ def main(argv=None) -> int:
     rows_list = [int(r) for r in ns.rows.split(",")]
     ctx = Fp4ArContext(max(rows_list), device=dev)
     common = {"kind": "timing", "tp": world, "hidden": N.HIDDEN, "graphK": ns.graph, "iters": ns.iters,
-              "warmup": ns.warmup, "tag": ns.tag, "gpu": torch.cuda.get_device_name(dev),
-              "nccl": ".".join(map(str, torch.cuda.nccl.version())), "time": time.strftime("%Y-%m-%dT%H:%M:%S")}
+              "warmup": ns.warmup, "tag": ns.tag, **run_info(dev)}
     records = []
 
     def emit(rec):

@@ -25,6 +25,7 @@ import torch.distributed as dist
 from .. import _native as N
 from .. import oracle as O
 from ..parallel.context import Fp4ArContext
+from ..utils.runinfo import sources_digest
 from .gate import CellConfig, Outputs, args_for, make_inputs, mismatches, rel_l2
 
 IN_NAMES = {"bf16": N.IN_BF16, "nvfp4": N.IN_NVFP4}
@@ -175,6 +176,7 @@ def main(argv=None) -> int:
                     rec = gate_cell(ctx, cfg, reps=ns.reps, graph_calls=ns.graph_calls, graph_reps=ns.graph_reps,
                                     skew_reps=ns.skew_reps, skew_us=ns.skew_us, negctl=ns.negctl)
                     rec["seconds"] = round(time.time() - t0, 2)
+                    rec["sources"] = sources_digest()
                     fails += not rec["pass"]
                     records.append(rec)
                     if rank == 0:
