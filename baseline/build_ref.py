@@ -26,16 +26,48 @@ def nccl_paths():
     return base / "include", base / "lib"
 
 
+def copy_sources(ref: str) -> Path | None:
+    src = OUT / "src"
+    if Path(ref).exists():
+        if src.exists():
+            shutil.rmtree(src)
+        shutil.copytree(ref, src, ignore=shutil.ignore_patterns(".git"))
+    return src if src.exists() else None
+
+
+def build_host_oracle(ref: str = "/root/reference", force: bool = False) -> Path | None:
+    """baseline/_ref/libref_oracle.so: the reference's own CPU oracle (bench/codec/codec_bench.cu, `namespace cpu`)
+    behind two C functions (baseline/ref_oracle_shim.cu).  Host code only runs; no GPU is needed to use it."""
+    out = OUT / "libref_oracle.so"
+    if out.exists() and not force:
+        return out
+    src = OUT / "src"
+    if not src.exists():
+        src = copy_sources(ref)
+    if src is None:
+        return None
+    OUT.mkdir(exist_ok=True)
+    cmd = ["nvcc", "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC,-fopenmp",
+           "-diag-suppress", "177,550", f"-I{src}", f"-I{src}/include", f"-I{src}/harness", str(HERE / "ref_oracle_shim.cu"),
+           "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        print(r.stdout[-2000:], r.stderr[-3000:], file=sys.stderr)
+        return None
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--host-oracle", action="store_true", help="build only the CPU oracle bridge")
     ns = ap.parse_args(argv)
-    src = OUT / "src"
-    if Path(ns.src).exists():
-        if src.exists():
-            shutil.rmtree(src)
-        shutil.copytree(ns.src, src, ignore=shutil.ignore_patterns(".git"))
-    if not src.exists():
+    if ns.host_oracle:
+        out = build_host_oracle(ns.src, force=True)
+        print(out if out else "failed")
+        return 0 if out else 1
+    src = copy_sources(ns.src)
+    if src is None:
         print("reference sources not found", file=sys.stderr)
         return 1
     inc, lib = nccl_paths()
