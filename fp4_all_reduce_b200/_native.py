@@ -123,6 +123,8 @@ def cuda() -> C.CDLL:
     lib.fp4ar_fill_sentinel.argtypes = [vp, C.c_size_t, C.c_int, vp]
     lib.fp4ar_selftest_scale_division.argtypes = [C.c_int, vp, vp]
     lib.fp4ar_selftest_scale_division.restype = C.c_int
+    lib.fp4ar_selftest_conversions.argtypes = [C.c_int, C.c_uint, C.c_uint, vp, vp]
+    lib.fp4ar_selftest_conversions.restype = C.c_int
     lib.fp4ar_gemm_nvfp4.argtypes = [C.POINTER(PushView), C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp, vp, vp]
     lib.fp4ar_gemm_nvfp4.restype = C.c_int
     lib.fp4ar_gemm_status.argtypes = [C.POINTER(StatusWords)]

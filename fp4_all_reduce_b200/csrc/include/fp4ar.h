@@ -131,6 +131,12 @@ int fp4ar_fill_sentinel(void* window, size_t buffer_bytes, int nbuffers, fp4ar_s
 /* Exhaustive check of the encoder's division-free multiplier for one exponent of the row-scale inverse (27..227):
  * adds the number of (mantissa, scale byte) cases that differ from IEEE division to *device_mismatch_counter. */
 int fp4ar_selftest_scale_division(int exp_biased, unsigned long long* device_mismatch_counter, fp4ar_stream stream);
+/* Exhaustive checks of the hardware conversions against plain software models; mismatches are added to the counter.
+ * which 0: E4M3 block scale of x / 6 for the non-negative FP32 bit patterns [first, first + count) (domain 0 .. 2^31);
+ * which 1: E2M1 value encode for the FP32 bit patterns [first, first + count) in every nibble position;
+ * which 2: E2M1 / E4M3 decode tables and the -0 canonicalisation (first, count ignored).  count 0 = to the end. */
+int fp4ar_selftest_conversions(int which, unsigned int first, unsigned int count,
+                               unsigned long long* device_mismatch_counter, fp4ar_stream stream);
 
 #ifdef __cplusplus
 }

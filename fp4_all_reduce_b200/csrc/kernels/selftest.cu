@@ -1,0 +1,146 @@
+// Exhaustive device self-tests of the conversion primitives the codec is built on, each against a plain software
+// model written out below (thresholds and bit arithmetic, no special instructions):
+//
+//   block scale   every non-negative FP32 x (and NaN): cvt.rn.satfinite.e4m3x2.f32(div6(x)) == soft_e4m3(x / 6)
+//                 with an IEEE division; covers the division-free div6 and the hardware E4M3 rounding
+//   value         every FP32 bit pattern: the nibble of cvt.rn.satfinite.e2m1x2.f32 == soft_e2m1(x), in each of the
+//                 eight positions of e2m1_pack8
+//   decode        every 16-bit pattern in either half of a word through e2m1_unpack8, every pair of scale bytes
+//                 through e4m3_unpack2, against tables; canon_neg0 on every 16-bit pattern in either half
+//
+// Each kernel adds its mismatch count to a counter; the host test expects 0.  Nothing here can fault: the kernels
+// only convert numbers held in registers.
+//
+// Reference project counterparts: tests T1, T3-T5 of bench/codec/codec_bench.cu:29-134 and tests/codec_test.cu:31-72.
+#include <cuda_runtime.h>
+#include "../include/fp4ar.h"
+#include "../include/fp4ar_codec.cuh"
+#include "host_util.h"
+
+namespace fp4ar {
+
+__device__ __forceinline__ uint32_t soft_e4m3(float x) {   // x >= 0 or NaN
+  if (x != x) return 0x7fu;
+  if (x >= 448.0f) return 0x7eu;
+  if (x < 0x1p-6f) return (uint32_t)rintf(x * 512.0f);     // subnormal grid, step 2^-9; 8 is the first normal
+  int e;
+  const float m = frexpf(x, &e);                           // x = m * 2^e, m in [0.5, 1)
+  int q = (int)rintf((2.0f * m - 1.0f) * 8.0f);
+  int E = e - 1;
+  if (q == 8) { q = 0; E += 1; }
+  const int byte = ((E + 7) << 3) | q;
+  return (uint32_t)(byte > 0x7e ? 0x7e : byte);
+}
+
+__device__ __forceinline__ uint32_t soft_e2m1(float x) {
+  if (x != x) return 7u;
+  const uint32_t sign = (__float_as_uint(x) >> 31) ? 8u : 0u;
+  const float a = fabsf(x);
+  uint32_t c;
+  if (a <= 0.25f) c = 0;
+  else if (a < 0.75f) c = 1;
+  else if (a <= 1.25f) c = 2;
+  else if (a < 1.75f) c = 3;
+  else if (a <= 2.5f) c = 4;
+  else if (a < 3.5f) c = 5;
+  else if (a <= 5.0f) c = 6;
+  else c = 7;
+  return sign | c;
+}
+
+__device__ __forceinline__ float soft_e2m1_value(uint32_t n) {
+  const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  const float v = mag[n & 7u];
+  return (n & 8u) ? -v : v;
+}
+__device__ __forceinline__ float soft_e4m3_value(uint32_t b) {
+  const int e = (b >> 3) & 15, m = b & 7;
+  float v = e ? ldexpf(1.0f + m / 8.0f, e - 7) : ldexpf(m / 8.0f, -6);
+  return (b & 0x80u) ? -v : v;
+}
+
+// u runs over [first, first + count) of non-negative FP32 bit patterns (0 .. 0x7fffffff: finite, +inf, NaNs)
+__global__ void selftest_block_scale_kernel(uint32_t first, uint32_t count, unsigned long long* mismatches) {
+  unsigned long long bad = 0;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+    const float x = __uint_as_float(first + i);
+    const uint32_t hw = e4m3_pack2(div6(x), 0.0f) & 0xffu;
+    const uint32_t sw = soft_e4m3(__fdiv_rn(x, 6.0f));
+    bad += hw != sw;
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
+// every FP32 bit pattern of [first, first + count), in nibble position (pattern & 7) of the packed word
+__global__ void selftest_e2m1_encode_kernel(uint32_t first, uint32_t count, unsigned long long* mismatches) {
+  unsigned long long bad = 0;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+    const uint32_t u = first + i;
+    const float x = __uint_as_float(u);
+    const int pos = (int)(u & 7u);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = (k == pos) ? x : 1.0f;      // 1.0 encodes as nibble 2 everywhere else
+    F2 a, b, c, d;
+    a.lo = v[0]; a.hi = v[1]; b.lo = v[2]; b.hi = v[3]; c.lo = v[4]; c.hi = v[5]; d.lo = v[6]; d.hi = v[7];
+    const uint32_t w = e2m1_pack8(a, b, c, d);
+    uint32_t want = 0x22222222u;
+    want = (want & ~(0xfu << (4 * pos))) | (soft_e2m1(x) << (4 * pos));
+    bad += w != want;
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
+// 2 x 65536 value words, 65536 scale pairs, 2 x 65536 canonicalisations
+__global__ void selftest_decode_kernel(unsigned long long* mismatches) {
+  unsigned long long bad = 0;
+  for (uint32_t p = blockIdx.x * blockDim.x + threadIdx.x; p < 65536u; p += gridDim.x * blockDim.x) {
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      const uint32_t w = half ? ((p << 16) | 0x2222u) : (p | 0x22220000u);
+      F2 out[4];
+      e2m1_unpack8(w, out);
+      const float got[8] = {out[0].lo, out[0].hi, out[1].lo, out[1].hi, out[2].lo, out[2].hi, out[3].lo, out[3].hi};
+#pragma unroll
+      for (int k = 0; k < 8; k++) bad += __float_as_uint(got[k]) != __float_as_uint(soft_e2m1_value((w >> (4 * k)) & 15u));
+      // canonicalisation: every -0 nibble becomes +0, nothing else changes
+      uint32_t want = w;
+#pragma unroll
+      for (int k = 0; k < 8; k++)
+        if (((w >> (4 * k)) & 15u) == 8u) want &= ~(0xfu << (4 * k));
+      bad += canon_neg0(w) != want;
+    }
+    const F2 s = e4m3_unpack2(p);
+    const uint32_t b0 = p & 0xffu, b1 = p >> 8;
+    const float w0 = soft_e4m3_value(b0), w1 = soft_e4m3_value(b1);
+    if ((b0 & 0x7fu) == 0x7fu) bad += !(s.lo != s.lo); else bad += __float_as_uint(s.lo) != __float_as_uint(w0);
+    if ((b1 & 0x7fu) == 0x7fu) bad += !(s.hi != s.hi); else bad += __float_as_uint(s.hi) != __float_as_uint(w1);
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
+}  // namespace fp4ar
+
+using namespace fp4ar;
+
+// which: 0 block scale (patterns 0 .. 0x7fffffff), 1 value encode (all 2^32 patterns), 2 decode / canonicalise tables.
+// For 0 and 1 the range [first, first + count) is tested (count 0 = up to the end of the domain).
+extern "C" int fp4ar_selftest_conversions(int which, unsigned int first, unsigned int count,
+                                          unsigned long long* device_mismatch_counter, fp4ar_stream stream) {
+  if (!device_mismatch_counter || which < 0 || which > 2) return FP4AR_ERR_ARGUMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = 8 * device_sm_count();
+  if (which == 0) {
+    if (first > 0x7fffffffu) return FP4AR_ERR_ARGUMENT;
+    const unsigned int room = 0x80000000u - first;
+    if (count == 0 || count > room) count = room;
+    selftest_block_scale_kernel<<<grid, 256, 0, st>>>(first, count, device_mismatch_counter);
+  } else if (which == 1) {
+    const unsigned long long room = 0x100000000ull - first;
+    if (count == 0 || count > room) count = (unsigned int)(room > 0xffffffffull ? 0xffffffffull : room);
+    selftest_e2m1_encode_kernel<<<grid, 256, 0, st>>>(first, count, device_mismatch_counter);
+  } else {
+    selftest_decode_kernel<<<256, 256, 0, st>>>(device_mismatch_counter);
+  }
+  return cuda_check_launch();
+}
