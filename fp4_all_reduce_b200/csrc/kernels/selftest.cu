@@ -13,13 +13,15 @@
 //
 // Reference project counterparts: tests T1, T3-T5 of bench/codec/codec_bench.cu:29-134 and tests/codec_test.cu:31-72.
 #include <cuda_runtime.h>
+#include <cmath>
+#include <cstring>
 #include "../include/fp4ar.h"
 #include "../include/fp4ar_codec.cuh"
 #include "host_util.h"
 
 namespace fp4ar {
 
-__device__ __forceinline__ uint32_t soft_e4m3(float x) {   // x >= 0 or NaN
+__host__ __device__ inline uint32_t soft_e4m3(float x) {   // x >= 0 or NaN
   if (x != x) return 0x7fu;
   if (x >= 448.0f) return 0x7eu;
   if (x < 0x1p-6f) return (uint32_t)rintf(x * 512.0f);     // subnormal grid, step 2^-9; 8 is the first normal
@@ -32,9 +34,9 @@ __device__ __forceinline__ uint32_t soft_e4m3(float x) {   // x >= 0 or NaN
   return (uint32_t)(byte > 0x7e ? 0x7e : byte);
 }
 
-__device__ __forceinline__ uint32_t soft_e2m1(float x) {
+__host__ __device__ inline uint32_t soft_e2m1(float x) {
   if (x != x) return 7u;
-  const uint32_t sign = (__float_as_uint(x) >> 31) ? 8u : 0u;
+  const uint32_t sign = signbit(x) ? 8u : 0u;
   const float a = fabsf(x);
   uint32_t c;
   if (a <= 0.25f) c = 0;
@@ -48,12 +50,12 @@ __device__ __forceinline__ uint32_t soft_e2m1(float x) {
   return sign | c;
 }
 
-__device__ __forceinline__ float soft_e2m1_value(uint32_t n) {
+__host__ __device__ inline float soft_e2m1_value(uint32_t n) {
   const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
   const float v = mag[n & 7u];
   return (n & 8u) ? -v : v;
 }
-__device__ __forceinline__ float soft_e4m3_value(uint32_t b) {
+__host__ __device__ inline float soft_e4m3_value(uint32_t b) {
   const int e = (b >> 3) & 15, m = b & 7;
   float v = e ? ldexpf(1.0f + m / 8.0f, e - 7) : ldexpf(m / 8.0f, -6);
   return (b & 0x80u) ? -v : v;
@@ -143,4 +145,20 @@ extern "C" int fp4ar_selftest_conversions(int which, unsigned int first, unsigne
     selftest_decode_kernel<<<256, 256, 0, st>>>(device_mismatch_counter);
   }
   return cuda_check_launch();
+}
+
+// The software models themselves, callable on the host, so that they can be checked against the host model of the
+// codec without a GPU.  what: 0 soft_e4m3 (x >= 0 or NaN), 1 soft_e2m1, 2 soft_e2m1_value, 3 soft_e4m3_value.
+extern "C" int fp4ar_selftest_soft_model(int what, const float* in, const unsigned int* in_bits, int n, unsigned int* out_bits) {
+  if (n < 0 || !out_bits) return FP4AR_ERR_ARGUMENT;
+  for (int i = 0; i < n; i++) {
+    switch (what) {
+      case 0: out_bits[i] = soft_e4m3(in[i]); break;
+      case 1: out_bits[i] = soft_e2m1(in[i]); break;
+      case 2: { const float v = soft_e2m1_value(in_bits[i]); memcpy(&out_bits[i], &v, 4); break; }
+      case 3: { const float v = soft_e4m3_value(in_bits[i]); memcpy(&out_bits[i], &v, 4); break; }
+      default: return FP4AR_ERR_ARGUMENT;
+    }
+  }
+  return FP4AR_OK;
 }

@@ -227,3 +227,41 @@ def test_benchmark_config0_two_simulated_ranks():
     assert 0.02 < rel < 0.2, rel
     rel2 = float(np.linalg.norm(R.bf16_to_f32(O.allreduce(xs, algo=1)["out"]) - exact) / np.linalg.norm(exact))
     assert rel < rel2 < 0.3
+
+
+def test_software_models_of_the_device_selftests_match_the_host_model():
+    """The plain software encoders / decoders that the exhaustive GPU self-tests compare the hardware with
+    (csrc/kernels/selftest.cu) agree with the host model on dense sweeps, so a GPU mismatch would point at the GPU side."""
+    import ctypes as C
+
+    from fp4_all_reduce_b200 import _native as NN
+
+    lib = NN.cuda()          # loading the library needs no GPU; only host functions are called
+    lib.fp4ar_selftest_soft_model.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    rng = np.random.default_rng(5)
+    # E4M3: every BF16-representable non-negative value, a dense log sweep, ties, the saturation edge, inf and NaN
+    bits = np.arange(0, 0x7f81, dtype=np.uint32) << 16
+    x = np.concatenate([bits.view(np.float32), np.exp(rng.uniform(-25, 8, 400000)).astype(np.float32),
+                        np.array([447.9, 448.0, 463.9, 464.0, 479.9, 480.0, 1e9, np.inf, np.nan, 2.0 ** -9, 2.0 ** -10,
+                                  1.5 * 2.0 ** -9, 2.5 * 2.0 ** -9], np.float32)])
+    out = np.zeros(x.size, np.uint32)
+    assert lib.fp4ar_selftest_soft_model(0, x.ctypes.data, None, x.size, out.ctypes.data) == 0
+    assert np.array_equal(out.astype(np.uint8), O.e4m3_encode(x))
+    # E2M1: all BF16 values of both signs, midpoints, random
+    allbf = (np.arange(0, 0x10000, dtype=np.uint32) << 16).view(np.float32)
+    y = np.concatenate([allbf, rng.normal(0, 3, 400000).astype(np.float32),
+                        np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -5.0, 6.0, 7.0, -0.0, 0.0], np.float32)])
+    out = np.zeros(y.size, np.uint32)
+    assert lib.fp4ar_selftest_soft_model(1, y.ctypes.data, None, y.size, out.ctypes.data) == 0
+    assert np.array_equal(out.astype(np.uint8), O.e2m1_encode(y))
+    # decode tables
+    n16 = np.arange(16, dtype=np.uint32)
+    out = np.zeros(16, np.uint32)
+    assert lib.fp4ar_selftest_soft_model(2, None, n16.ctypes.data, 16, out.ctypes.data) == 0
+    assert np.array_equal(out, O.e2m1_table().view(np.uint32))
+    n256 = np.arange(256, dtype=np.uint32)
+    out = np.zeros(256, np.uint32)
+    assert lib.fp4ar_selftest_soft_model(3, None, n256.ctypes.data, 256, out.ctypes.data) == 0
+    tab = O.e4m3_table()
+    finite = ~np.isnan(tab)
+    assert np.array_equal(out[finite], tab.view(np.uint32)[finite])
