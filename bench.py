@@ -166,7 +166,7 @@ def main() -> int:
     # Any failure or inconsistency keeps the serial number above.
     try:
         copy_stream = torch.cuda.Stream(device=dev)
-        main = torch.cuda.current_stream(dev)
+        main_stream = torch.cuda.current_stream(dev)
         xs = [torch.empty_like(chain.partials[0]) for _ in range(2)]
         rs = [torch.empty_like(chain.residual) for _ in range(2)]
         ready = [torch.cuda.Event() for _ in range(2)]
@@ -183,17 +183,17 @@ def main() -> int:
             issue(0)
             for i in range(nsteps):
                 sl = i & 1
-                main.wait_event(ready[sl])
+                main_stream.wait_event(ready[sl])
                 chain.partials[0].copy_(xs[sl], non_blocking=True)
                 chain.residual.copy_(rs[sl], non_blocking=True)
-                freed[sl].record(main)
+                freed[sl].record(main_stream)
                 if i + 1 < nsteps:
                     issue((i + 1) & 1)
                 graph.replay()
                 outh.copy_(chain.out[0, :16], non_blocking=True)
 
         for sl in range(2):
-            freed[sl].record(main)
+            freed[sl].record(main_stream)
         run(2)
         torch.cuda.synchronize(dev)
         timing.align_ranks(dev)
