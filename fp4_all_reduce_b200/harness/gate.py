@@ -13,11 +13,14 @@ the multi-phase protocol on one (ranks, algorithm, input, epilogue, rows) cell:
   5. calls with one rank delayed by a spin kernel, the delayed rank rotating.
 
 Negative controls: `negctl="stale"` feeds the kernel the next input set while the expectation uses the
-current one, `negctl="flip"` flips one bit of one rank's output before the compare; both must turn
+current one, `negctl="flip"` flips one bit of one rank's output before the compare, `negctl="bias"` (norm
+epilogues) runs the kernel with the weight bias shifted by 2^-7 against the unshifted expectation; all must turn
 every phase red.  This is the protocol of the reference project's harness (harness/fp4ar_bench.cu:248-347
 and tests/negative_control.sh:11-18) re-stated for one-process-per-GPU groups and for the emulated group.
 """
 from __future__ import annotations
+
+import dataclasses
 
 from dataclasses import dataclass, field
 from typing import Optional
@@ -167,9 +170,11 @@ def gate_cell_emulated(cfg: CellConfig, *, reps: int = 30, graph_calls: int = 5,
         sets = [make_inputs(cfg, s, dev) for s in range(3)]
         outs = Outputs(cfg, dev, cfg.nranks)
 
+        launch_cfg = dataclasses.replace(cfg, weight_bias=cfg.weight_bias + 2.0 ** -7) if negctl == "bias" else cfg
+
         def call(s: int):
             src = sets[(s + 1) % 3] if negctl == "stale" else sets[s % 3]
-            g.launch([args_for(cfg, src, outs, r, r) for r in range(cfg.nranks)])
+            g.launch([args_for(launch_cfg, src, outs, r, r) for r in range(cfg.nranks)])
 
         def compare(s: int) -> int:
             torch.cuda.synchronize()

@@ -14,6 +14,7 @@ negative control can be recognised by its exit code), as in the reference harnes
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import sys
@@ -39,9 +40,11 @@ def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int
     sets = [make_inputs(cfg, s, dev) for s in range(3)]
     outs = Outputs(cfg, dev, 1)
 
+    launch_cfg = dataclasses.replace(cfg, weight_bias=cfg.weight_bias + 2.0 ** -7) if negctl == "bias" else cfg
+
     def call(s: int):
         src = sets[(s + 1) % 3] if negctl == "stale" else sets[s % 3]
-        ctx.launch(args_for(cfg, src, outs, 0, rank))
+        ctx.launch(args_for(launch_cfg, src, outs, 0, rank))
 
     def compare(s: int) -> int:
         torch.cuda.synchronize()
@@ -150,7 +153,7 @@ def main(argv=None) -> int:
     ap.add_argument("--graph-reps", type=int, default=10)
     ap.add_argument("--skew-reps", type=int, default=8)
     ap.add_argument("--skew-us", type=float, default=50.0)
-    ap.add_argument("--negctl", default=None, choices=[None, "stale", "flip"])
+    ap.add_argument("--negctl", default=None, choices=[None, "stale", "flip", "bias"])
     ap.add_argument("--timeout-ms", type=int, default=1000)
     ap.add_argument("--out", default=None)
     ns = ap.parse_args(argv)

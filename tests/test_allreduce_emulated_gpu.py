@@ -98,3 +98,11 @@ def test_two_shot_pipeline_depths(P, lags):
     for rows, epi in ((700, 0), (37, 1)):
         rec = gate_cell_emulated(CellConfig(nranks=P, rows=rows, epilogue=epi, lags=lags), reps=4, graph_calls=3, graph_reps=2)
         assert rec["pass"], (lags, rows, rec)
+
+
+def test_norm_weight_bias_negative_control_turns_the_gate_red():
+    """The fused-norm gate notices a weight bias that is off by 2^-7 (the reference's LN_NEGCTL control,
+    bench/fused_norm/drv_norm.cu:188)."""
+    rec = gate_cell_emulated(CellConfig(nranks=2, rows=96, epilogue=1), reps=3, graph_calls=2, graph_reps=2, negctl="bias")
+    assert not rec["pass"]
+    assert rec["mism_first"] > 0
