@@ -25,6 +25,7 @@ scripts/run_cell.sh:9-26 one cell with time limit and clock abort, scripts/gpuru
     with exit code 3 ("CLOCK_ABORT") when it differs -- the guard only reads, it never sets a clock;
   * after a cell, its records are scanned for thermal / hardware slow-down reasons; such a cell is run once more
     and the first attempt is kept with the suffix `.rejected`;
+  * JSON lines that a program only prints (no --out option) are copied from its log into `<out>/<cell>.jsonl`;
   * `<out>/campaign_state.jsonl` has one line per finished attempt; --resume skips cells that already ended
     with exit code 0.
 """
@@ -202,6 +203,23 @@ def run_with_limit(cmd: list[str], env: dict, log_path: str, limit_s: float, gra
     return rc, time.time() - t0, timed_out
 
 
+def harvest_records(log_path: str, start: int, jsonl_path: str) -> int:
+    """Programs without an --out option print their records: copy the JSON lines this attempt wrote to the log into
+    <cell>.jsonl unless the program produced that file itself.  Returns the number of lines copied."""
+    if os.path.exists(jsonl_path):
+        return 0
+    try:
+        with open(log_path) as f:
+            f.seek(start)
+            lines = [l for l in f if l.startswith("{") and l.rstrip().endswith("}")]
+    except OSError:
+        return 0
+    if lines:
+        with open(jsonl_path, "w") as f:
+            f.writelines(lines)
+    return len(lines)
+
+
 def slowdown_reasons(jsonl_path: str) -> list[str]:
     bad = set()
     try:
@@ -308,7 +326,9 @@ def run_campaign(cells: list[Cell], out_dir: str, *, deadline: float = 0.0, resu
             jsonl = os.path.join(out_dir, cell.name + ".jsonl")
             for attempt in (1, 2):
                 echo(f"START {cell.name} gpus={gpus} limit={cell.timeout_s}s attempt={attempt}")
+                log_start = os.path.getsize(log_path) if os.path.exists(log_path) else 0
                 rc, secs, tmo = run_with_limit(cmd, env, log_path, cell.timeout_s)
+                harvest_records(log_path, log_start, jsonl)
                 bad = slowdown_reasons(jsonl)
                 rec = {"cell": cell.name, "rc": rc, "seconds": round(secs, 1), "timed_out": tmo, "attempt": attempt,
                        "slowdown": bad, "gpus": gpus, "time": now()}

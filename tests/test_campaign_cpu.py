@@ -56,6 +56,7 @@ def test_campaign_runs_times_out_and_resumes(tmp_path):
     assert st["a"]["rc"] == 0 and st["b"]["rc"] == 7
     assert st["c"]["rc"] == 124 and st["c"]["timed_out"] is True and st["c"]["seconds"] < 20
     assert "hello" in open(os.path.join(out, "a.log")).read()
+    assert not os.path.exists(os.path.join(out, "a.jsonl"))            # nothing that looks like a record was printed
     assert os.listdir(str(tmp_path / "locks")) == []          # every lock released
     # resume: only the failed cells run again
     msgs.clear()
@@ -183,3 +184,11 @@ def test_clock_control_lock_reset_guard_against_fake_nvml(tmp_path, monkeypatch)
     assert cc3.guard(10.0, 3996, now=lambda: next(t))["state"] == K.RESET_VERIFIED
     assert nv3.clk == [3996]
     assert "guard fired" in open(os.path.join(str(tmp_path / "c"), "CLOCK.log")).read()
+
+
+def test_printed_records_are_harvested(tmp_path):
+    child = _write_child(tmp_path, "p.py", "print('noise'); print('{\"op\": \"x\", \"us\": 1.5}'); print('{broken')\n")
+    out = str(tmp_path / "runs")
+    assert C.run_campaign(C.parse_cells(f"p 1 30 -- {child}\n"), out, echo=lambda m: None) == 0
+    lines = open(os.path.join(out, "p.jsonl")).read().splitlines()
+    assert [json.loads(l) for l in lines] == [{"op": "x", "us": 1.5}]
