@@ -192,3 +192,22 @@ def test_printed_records_are_harvested(tmp_path):
     assert C.run_campaign(C.parse_cells(f"p 1 30 -- {child}\n"), out, echo=lambda m: None) == 0
     lines = open(os.path.join(out, "p.jsonl")).read().splitlines()
     assert [json.loads(l) for l in lines] == [{"op": "x", "us": 1.5}]
+
+
+def test_shipped_cell_files_parse_and_name_real_programs():
+    import importlib.util
+    from pathlib import Path
+
+    root = Path(C.__file__).resolve().parent
+    files = sorted((root / "cells").glob("*.txt"))
+    assert len(files) >= 4
+    for f in files:
+        cells = C.parse_cells(f.read_text())
+        assert cells, f
+        for c in cells:
+            if c.program.endswith(".py"):
+                assert (root.parent.parent / c.program).exists(), (f.name, c.program)
+            else:
+                assert c.program in C.HARNESS_MODULES, (f.name, c.program)
+                assert importlib.util.find_spec(f"fp4_all_reduce_b200.harness.{c.program}") is not None
+            assert c.gpus in (1, 2, 4, 8) and 30 <= c.timeout_s <= 900
