@@ -106,3 +106,16 @@ def test_norm_weight_bias_negative_control_turns_the_gate_red():
     rec = gate_cell_emulated(CellConfig(nranks=2, rows=96, epilogue=1), reps=3, graph_calls=2, graph_reps=2, negctl="bias")
     assert not rec["pass"]
     assert rec["mism_first"] > 0
+
+
+@pytest.mark.skipif(__import__("os").environ.get("FP4AR_RUN_UNVERIFIED") != "1",
+                    reason="wider depth x input x epilogue matrix, first run pending; set FP4AR_RUN_UNVERIFIED=1")
+@pytest.mark.parametrize("P", [4, 8])
+@pytest.mark.parametrize("lags", [33, 50, 66, 67])
+@pytest.mark.parametrize("inp,epi", [(N.IN_NVFP4, 0), (N.IN_NVFP4, 1), (N.IN_BF16, 2), (N.IN_NVFP4, 3)])
+def test_two_shot_pipeline_depths_all_inputs_and_epilogues(P, lags, inp, epi):
+    """Depth pairs x NVFP4 input x every epilogue with several rows per team (the record ring is one slot longer with
+    NVFP4 input, and the quantised epilogues stage differently sized rows)."""
+    rec = gate_cell_emulated(CellConfig(nranks=P, rows=900, input=inp, epilogue=epi, lags=lags), reps=4, graph_calls=3,
+                             graph_reps=2)
+    assert rec["pass"], (P, lags, inp, epi, rec)
