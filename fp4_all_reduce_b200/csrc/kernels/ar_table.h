@@ -9,7 +9,12 @@ struct ArKernelEntry {
   int P, algo, input, epi, T;
   const void* fn;
   int team_bytes, cta_extra, max_teams;
+  int variant;      // 0 = the product kernel; other values are experimental builds of the same template
 };
+
+#ifndef FP4AR_KERNEL_VARIANT_ID
+#define FP4AR_KERNEL_VARIANT_ID 0
+#endif
 
 constexpr int kDefaultTeamWarps = 3;   // warps per row team unless a launch asks for another compiled width
 
@@ -18,8 +23,9 @@ inline ArKernelEntry make_entry() {
   using S = ArShape<P, ALGO, IN, EPI, T>;
   ArKernelEntry e;
   e.P = P; e.algo = ALGO; e.input = IN; e.epi = EPI; e.T = T;
-  e.fn = reinterpret_cast<const void*>(&ar_kernel<P, ALGO, IN, EPI, T>);
+  e.fn = reinterpret_cast<const void*>(&FP4AR_KERNEL_NAME<P, ALGO, IN, EPI, T>);
   e.team_bytes = S::kTeamBytes; e.cta_extra = S::kCtaExtra; e.max_teams = S::kMaxTeams;
+  e.variant = FP4AR_KERNEL_VARIANT_ID;
   return e;
 }
 
@@ -32,5 +38,6 @@ void ar_register_p4b(ArKernelEntry* out, int* n);
 void ar_register_p8(ArKernelEntry* out, int* n);
 void ar_register_p8b(ArKernelEntry* out, int* n);
 void ar_register_cmp(ArKernelEntry* out, int* n);
+void ar_register_cold(ArKernelEntry* out, int* n);   // variant 1: slow poll paths out of line (ar_inst_cold.cu)
 
 }  // namespace fp4ar

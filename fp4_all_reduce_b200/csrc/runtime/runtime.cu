@@ -65,14 +65,27 @@ static std::vector<ArKernelEntry>& kernel_table() {
     ar_register_p1(buf, &n); ar_register_p2(buf, &n); ar_register_p2b(buf, &n);
     ar_register_p4(buf, &n); ar_register_p4b(buf, &n); ar_register_p8(buf, &n); ar_register_p8b(buf, &n);
     ar_register_cmp(buf, &n);
+    ar_register_cold(buf, &n);
     table.assign(buf, buf + n);
   });
   return table;
 }
-static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi, int T) {
+static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi, int T, int variant = 0) {
   for (const ArKernelEntry& e : kernel_table())
-    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi && e.T == T) return &e;
+    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi && e.T == T && e.variant == variant) return &e;
   return nullptr;
+}
+// Experimental kernel builds: bits 8-15 of tune[1] if set, else FP4AR_KERNEL_VARIANT from the environment, else 0 (the
+// product kernels).  A shape that the variant does not provide falls back to the product kernel.
+static int kernel_variant_for(const fp4ar_args& a) {
+  const int from_call = (a.tune[1] >> 8) & 255;
+  if (from_call) return from_call;
+  static const int from_env = [] {
+    const char* s = std::getenv("FP4AR_KERNEL_VARIANT");
+    const int v = s ? std::atoi(s) : 0;
+    return v > 0 && v < 256 ? v : 0;
+  }();
+  return from_env;
 }
 // Team width: tune[2] of the call if set, else FP4AR_TEAM_WARPS from the environment, else the default.
 static int team_warps_for(const fp4ar_args& a) {
@@ -260,6 +273,10 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (c->nranks == 1) algo = FP4AR_ALGO_ONESHOT;
   const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, team_warps_for(a0));
   if (!ke) return FP4AR_ERR_UNSUPPORTED;
+  if (const int variant = kernel_variant_for(a0)) {
+    const ArKernelEntry* kv = find_kernel(c->nranks, algo, a0.input, a0.epilogue, ke->T, variant);
+    if (kv) ke = kv;
+  }
 
   ArParams prm;
   std::memset(&prm, 0, sizeof(prm));

@@ -63,10 +63,13 @@ class Cell:
         self.outq = torch.empty(rows, nb, dtype=torch.uint8, device=dev) if epi >= 2 else None
         self.rows, self.kind, self.epi = rows, kind, epi
 
+    variant = 0
+
     def args(self, i, mode, algo, teams, tw, rows=None, lags=0):
         return make_args(x=self.xs[i % self.nsets], out=self.out, rows=self.rows if rows is None else rows, mode=mode,
                          algo=algo, input=self.kind, epilogue=self.epi, gs=self.gs, res_in=self.res, res_out=self.res,
-                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw, lags=lags)
+                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw, lags=lags,
+                         variant=self.variant)
 
 
 def main(argv=None) -> int:
@@ -79,6 +82,7 @@ def main(argv=None) -> int:
     ap.add_argument("--team-warps", default="0")
     ap.add_argument("--teams", default="0")
     ap.add_argument("--lags", default="0", help="two-shot depths, comma list of lag_owner+16*lag_finish (e.g. 33 = 1,2; 50 = 2,3; 66 = 2,4)")
+    ap.add_argument("--variant", type=int, default=0, help="experimental kernel build (0 = product kernels)")
     ap.add_argument("--graph", type=int, default=10)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
@@ -118,6 +122,7 @@ def main(argv=None) -> int:
         for inp in ns.inputs.split(","):
             for epi in (int(e) for e in ns.epilogues.split(",")):
                 cell = Cell(rows, INPUTS[inp], epi, rank, world, dev)
+                cell.variant = ns.variant
                 for algo in ns.algos.split(","):
                     for tw in (int(t) for t in ns.team_warps.split(",")):
                         for teams, lags in ((int(t), int(l)) for t in ns.teams.split(",") for l in ns.lags.split(",")):
@@ -131,7 +136,7 @@ def main(argv=None) -> int:
                                 res[mode] = t["med_us"]
                                 st = ctx.status()
                                 emit({**common, "variant": "fp4ar", "mode": mode, "algo": algo, "rows": rows,
-                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags,
+                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags, "kernel_variant": ns.variant,
                                       "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
                                       "p90_us": round(t["p90_us"], 3), "sm_mhz": c.get("sm_mhz"),
                                       "reasons": c.get("reasons"), "status": st.describe(),

@@ -47,6 +47,7 @@ class CellConfig:
     qscale: float = 168.0
     teams: int = 0
     lags: int = 0                  # two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default)
+    variant: int = 0               # experimental kernel build (0 = product kernels)
 
     def resolved_algo(self) -> int:
         if self.nranks == 1:
@@ -129,7 +130,7 @@ class Outputs:
 def args_for(cfg: CellConfig, inp: InputSet, outs: Outputs, local: int, rank: int, mode=N.MODE_FUSED) -> N.Args:
     return make_args(x=inp.xs[rank], out=outs.out[local], rows=cfg.rows, mode=mode, algo=cfg.algo, input=cfg.input,
                      epilogue=cfg.epilogue, gs=inp.gs, res_in=inp.res, res_out=outs.res_out[local], weight=inp.weight,
-                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags)
+                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags, variant=cfg.variant)
 
 
 def _mism(t: Optional[torch.Tensor], want: Optional[np.ndarray]) -> int:
