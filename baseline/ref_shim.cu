@@ -22,6 +22,7 @@
 #include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
 #include <cstring>
 #include <mutex>
 #include <random>
@@ -34,6 +35,7 @@
 #include <nccl.h>
 #include "fp4ar_api.h"
 #include "lnorm_epi.cuh"
+#include "ref.cuh"   // the reference harness' own input quantiser (ref::q_encode) for --input nvfp4
 
 const Fp4ArVariant* fp4ar_register_L2();
 const Fp4ArVariant* fp4ar_register_L4();
@@ -57,6 +59,7 @@ struct Opts {
 };
 static Opts g;
 static std::vector<std::vector<float>> g_times;   // [rank][iter] ms
+static float g_gs[8] = {1, 1, 1, 1, 1, 1, 1, 1};   // --input nvfp4: static scale of every rank's partial (amax / 2688)
 static constexpr int H = 6144;
 
 static std::vector<uint16_t> read_file(const std::string& p, size_t n) {
@@ -107,6 +110,21 @@ static void worker(int rank, ncclUniqueId id, HostBarrier* bar, std::vector<char
   Fp4ArArgs a{}; a.x = x; a.out = out; a.rows = g.rows; a.hidden = H; a.mode = FP4AR_FUSED;
   a.algo = g.algo >= 0 ? g.algo : (g.tp == 2 ? FP4AR_ONESHOT : (norm ? FP4AR_ONESHOT : FP4AR_TWOSHOT));
   for (int r = 0; r < 8; r++) a.gs[r] = 1.0f;
+  if (g.input == "nvfp4") {
+    // The way the reference harness emulates calibration (harness/fp4ar_bench.cu:206-215): gs = amax of the rank's
+    // partial / 2688, known to every rank; the partial is quantised once, outside the timed region, by the
+    // reference's own ref::q_encode, and the kernels read the 3456-byte rows from a local buffer.
+    float am = 0.f;
+    for (size_t i = 0; i < n; i++) { uint32_t u = (uint32_t)hx[i] << 16; float f; memcpy(&f, &u, 4); f = fabsf(f); if (f == f && f > am) am = f; }
+    g_gs[rank] = (am > 0.f ? am : 1.f) / 2688.f;
+    bar->wait();
+    for (int r = 0; r < g.tp; r++) a.gs[r] = g_gs[r];
+    char* xq; CK(cudaMalloc(&xq, (size_t)g.rows * 3456));
+    ref::q_encode<<<2048, 256, 0, st>>>(x, xq, g.rows, g_gs[rank]);
+    CK(cudaStreamSynchronize(st));
+    a.xq = (const uint8_t*)xq; a.xq_in_window = 0;
+    if (rank == 0 && !g.dump.empty()) write_file(g.dump + ".gs.bin", g_gs, sizeof(float) * g.tp);
+  }
   lne::NormArgs na{}; na.res_in = res; na.res_out = res; na.w = w; na.eps = 1e-6f; na.wbias = 1.0f; na.epi = g.epi; na.outq = nullptr; na.qscale = 168.0f;
   auto op = [&]() { int r2 = norm ? lnorm_launch(&ctx, &a, &na, st) : V->launch(&ctx, &a, st); if (r2) { fprintf(stderr, "launch rejected on rank %d\n", rank); _exit(9); } };
   auto align = [&]() { CK(cudaStreamSynchronize(st)); bar->wait(); NK(ncclAllReduce(one, one, 1, ncclFloat, ncclSum, comm, st)); CK(cudaStreamSynchronize(st)); };
@@ -143,7 +161,8 @@ int main(int argc, char** argv) {
   int ndev = 0; CK(cudaGetDeviceCount(&ndev));
   if (g.tp < 2 || g.tp > ndev || (g.tp != 2 && g.tp != 4)) { printf("{\"impl\": \"reference\", \"unavailable\": \"reference push kernels support 2 or 4 ranks; asked for %d with %d GPUs visible\"}\n", g.tp, ndev); return 0; }
   if (g.variant != "L2" && g.variant != "L4" && g.variant != "lnorm") { fprintf(stderr, "variant must be L2, L4 or lnorm\n"); return 2; }
-  if (g.input != "bf16") { fprintf(stderr, "this driver feeds BF16 input only\n"); return 2; }
+  if (g.input != "bf16" && g.input != "nvfp4") { fprintf(stderr, "--input must be bf16 or nvfp4\n"); return 2; }
+  if (g.input == "nvfp4" && g.variant == "lnorm" && g.tp != 2) { printf("{\"impl\": \"reference\", \"unavailable\": \"the reference's fused norm kernel takes NVFP4 input at 2 ranks only\"}\n"); return 0; }
   size_t wb = g.variant == "lnorm" ? lnorm_window_bytes(g.rows, H, g.tp)
               : (g.variant == "L2" ? fp4ar_register_L2() : fp4ar_register_L4())->window_bytes(g.rows, H, g.tp);
   if (!wb) { printf("{\"impl\": \"reference\", \"unavailable\": \"variant %s has no window layout for %d ranks\"}\n", g.variant.c_str(), g.tp); return 0; }
@@ -157,9 +176,9 @@ int main(int argc, char** argv) {
   std::vector<float> mx(g.iters);
   for (int i = 0; i < g.iters; i++) { float m = 0; for (int r = 0; r < g.tp; r++) m = std::max(m, g_times[r][i]); mx[i] = m * 1000.f / g.graph; }
   std::sort(mx.begin(), mx.end());
-  printf("{\"impl\": \"reference\", \"variant\": \"%s\", \"tp\": %d, \"rows\": %d, \"epi\": %d, \"graphK\": %d, \"iters\": %d, \"warmup\": %d, "
+  printf("{\"impl\": \"reference\", \"variant\": \"%s\", \"input\": \"%s\", \"tp\": %d, \"rows\": %d, \"epi\": %d, \"graphK\": %d, \"iters\": %d, \"warmup\": %d, "
          "\"med_us\": %.3f, \"p10_us\": %.3f, \"p90_us\": %.3f, \"window_bytes\": %zu}\n",
-         g.variant.c_str(), g.tp, g.rows, g.epi, g.graph, g.iters, g.warmup, mx[g.iters / 2], mx[g.iters / 10], mx[(g.iters * 9) / 10], wb);
+         g.variant.c_str(), g.input.c_str(), g.tp, g.rows, g.epi, g.graph, g.iters, g.warmup, mx[g.iters / 2], mx[g.iters / 10], mx[(g.iters * 9) / 10], wb);
   fflush(stdout);
   _exit(0);   // the reference harness leaves the same way: NCCL / driver teardown can hang after graph capture
 }

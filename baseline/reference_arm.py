@@ -1,8 +1,9 @@
 """Run the reference project's own kernels (built by baseline/build_ref.py) on this machine.
 
-    python baseline/reference_arm.py check  [--tp 2] [--rows 512]     bit-compare the reference's L2 / L4 output with
-                                                                       this repository's host model on the same inputs
-    python baseline/reference_arm.py sweep  [--tp 2] [--out ref.jsonl] latency of L2 / L4 / lnorm at 1K..16K rows
+    python baseline/reference_arm.py check  [--tp 2] [--rows 512] [--input bf16|nvfp4]
+                                  bit-compare the reference's L2 / L4 output with this repository's host model
+    python baseline/reference_arm.py sweep  [--tp 2] [--out ref.jsonl] [--input bf16|nvfp4]
+                                  latency of L2 / L4 / lnorm at 1K..16K rows
 
 The binary runs all ranks as threads of one process on GPUs 0..tp-1.
 """
@@ -34,7 +35,7 @@ def run_shim(args, timeout=300):
     return {"impl": "reference", "unavailable": f"driver exited with code {p.returncode}: {(p.stderr or p.stdout)[-300:]}"}
 
 
-def check(tp: int, rows: int) -> int:
+def check(tp: int, rows: int, input_kind: str = "bf16") -> int:
     from fp4_all_reduce_b200 import oracle as O
     from fp4_all_reduce_b200.utils import data as D
 
@@ -48,26 +49,32 @@ def check(tp: int, rows: int) -> int:
             if variant == "L4" and tp != 4:
                 continue
             rec = run_shim(["--tp", tp, "--variant", variant, "--rows", rows, "--algo", algo, "--graph", 2, "--iters", 3,
-                            "--warmup", 1, "--in", pre, "--dump", pre])
+                            "--warmup", 1, "--in", pre, "--dump", pre, "--input", input_kind])
             if "unavailable" in rec:
                 print(json.dumps(rec)); return 1
             got = np.fromfile(f"{pre}.out.bin", dtype=np.uint16).reshape(rows, 6144)
-            want = O.allreduce(xs, algo=algo)["out"]
+            if input_kind == "nvfp4":
+                # the driver's static scales (amax / 2688 per rank) and this repository's static-scale quantiser
+                gs = [float(v) for v in np.fromfile(f"{pre}.gs.bin", dtype=np.float32)[:tp]]
+                want = O.allreduce([O.encode_static(x, g) for x, g in zip(xs, gs)], algo=algo, input_kind=1, gs=gs)["out"]
+            else:
+                want = O.allreduce(xs, algo=algo)["out"]
             mism = int(np.count_nonzero(got != want))
             ok &= mism == 0
-            print(json.dumps({"kind": "reference_vs_host_model", "variant": variant, "algo": algo, "tp": tp, "rows": rows,
-                              "mismatches": mism}))
+            print(json.dumps({"kind": "reference_vs_host_model", "variant": variant, "input": input_kind, "algo": algo, "tp": tp,
+                              "rows": rows, "mismatches": mism}))
     return 0 if ok else 3
 
 
-def sweep(tp: int, out: str | None) -> int:
+def sweep(tp: int, out: str | None, input_kind: str = "bf16") -> int:
     recs = []
     for rows in (1024, 2048, 4096, 8192, 16384):
         cases = [("L2", 0, 0)] if tp == 2 else [("L4", 1, 0), ("L4", 0, 0)]
-        cases += [("lnorm", 0, 1)]
+        if input_kind == "bf16" or tp == 2:      # the reference's fused norm takes NVFP4 input at 2 ranks only
+            cases += [("lnorm", 0, 1)]
         for variant, algo, epi in cases:
             rec = run_shim(["--tp", tp, "--variant", variant, "--rows", rows, "--algo", algo, "--epi", epi, "--graph", 10,
-                            "--iters", 30, "--warmup", 5])
+                            "--iters", 30, "--warmup", 5, "--input", input_kind])
             rec["algo"] = algo
             recs.append(rec)
             print(json.dumps(rec), flush=True)
@@ -84,5 +91,6 @@ if __name__ == "__main__":
     ap.add_argument("--tp", type=int, default=2)
     ap.add_argument("--rows", type=int, default=512)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--input", default="bf16", choices=["bf16", "nvfp4"])
     ns = ap.parse_args()
-    sys.exit(check(ns.tp, ns.rows) if ns.cmd == "check" else sweep(ns.tp, ns.out))
+    sys.exit(check(ns.tp, ns.rows, ns.input) if ns.cmd == "check" else sweep(ns.tp, ns.out, ns.input))

@@ -10,7 +10,8 @@ Cell file, one cell per line ('#' and blank lines ignored):
 
 <program> is a harness module name (bench_cli, gate_dist, gemm_ar_bench, micro, ops_bench, gemm_bench,
 nccl_tuned, ...), a dotted module path, or a path to a .py file.  With <gpus> > 1 the cell is started through
-`python -m torch.distributed.run` with one process per GPU on 127.0.0.1.  `--out <out>/<cell>.jsonl --tag <cell>`
+`python -m torch.distributed.run` with one process per GPU on 127.0.0.1, unless the cell says `LAUNCH=single` among
+its variables (a program that drives all of its GPUs from one process).  `--out <out>/<cell>.jsonl --tag <cell>`
 is appended for harness modules that take them, so every record carries its cell name.
 
 Behaviour, after the reference project's cluster scripts (scripts/driver.sh:8-17 cell loop with deadline,
@@ -103,7 +104,7 @@ def build_command(cell: Cell, out_dir: str, port: int, python: str = sys.executa
         extra += ["--out", os.path.join(out_dir, cell.name + ".jsonl")]
     if short in TAKES_OUT_TAG and "--tag" not in cell.args:
         extra += ["--tag", cell.name]
-    if cell.gpus > 1 and short not in SELF_LAUNCHING:
+    if cell.gpus > 1 and short not in SELF_LAUNCHING and cell.env.get("LAUNCH") != "single":
         head = [python, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={cell.gpus}",
                 "--master-addr", "127.0.0.1", "--master-port", str(port)]
     else:

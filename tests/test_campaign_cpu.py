@@ -35,6 +35,8 @@ nt     2 60  -- nccl_tuned --nproc 2
     assert C.build_command(cells[2], str(tmp_path), 1, python="py") == ["py", "some/script.py", "--x", "1"]
     assert C.build_command(cells[3], str(tmp_path), 1, python="py")[-3:] == ["-m", "pkg.mod", "--y"]
     assert "torch.distributed.run" not in C.build_command(cells[4], str(tmp_path), 1, python="py")
+    single = C.parse_cells("s 4 60 LAUNCH=single -- some/driver.py --tp 4")[0]
+    assert C.build_command(single, str(tmp_path), 1, python="py") == ["py", "some/driver.py", "--tp", "4"]
     with pytest.raises(ValueError):
         C.parse_cells("a 1 10 bench_cli")            # no '--'
     with pytest.raises(ValueError):
