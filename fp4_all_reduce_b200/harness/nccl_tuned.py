@@ -4,7 +4,7 @@
 
 NCCL reads NCCL_PROTO / NCCL_ALGO / NCCL_MIN_NCHANNELS when a communicator is created, so every configuration
 runs in its own torchrun job (this program launches them one after another and keeps, per row count, the best
-median).  Configurations: library defaults; Ring with LL128 / Simple and 16, 32, 64 channels; NVLS on and off.
+median).  Configurations: library defaults; Ring with LL128 / Simple and 64 channels; NVLS forced and off.
 The reference tunes the same knobs (harness/fp4ar_bench.cu:441-476, docs/RESULTS.md:89-97).
 """
 from __future__ import annotations
@@ -17,9 +17,7 @@ import sys
 
 CONFIGS = [
     {},
-    {"NCCL_ALGO": "Ring", "NCCL_PROTO": "LL128", "NCCL_MIN_NCHANNELS": "32"},
     {"NCCL_ALGO": "Ring", "NCCL_PROTO": "LL128", "NCCL_MIN_NCHANNELS": "64"},
-    {"NCCL_ALGO": "Ring", "NCCL_PROTO": "Simple", "NCCL_MIN_NCHANNELS": "32"},
     {"NCCL_ALGO": "Ring", "NCCL_PROTO": "Simple", "NCCL_MIN_NCHANNELS": "64"},
     {"NCCL_ALGO": "NVLS"},
     {"NCCL_NVLS_ENABLE": "0"},
