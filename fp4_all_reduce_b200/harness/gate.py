@@ -48,6 +48,7 @@ class CellConfig:
     teams: int = 0
     lags: int = 0                  # two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default)
     variant: int = 0               # experimental kernel build (0 = product kernels)
+    team_warps: int = 0            # warps per row team (0 = default)
 
     def resolved_algo(self) -> int:
         if self.nranks == 1:
@@ -130,7 +131,8 @@ class Outputs:
 def args_for(cfg: CellConfig, inp: InputSet, outs: Outputs, local: int, rank: int, mode=N.MODE_FUSED) -> N.Args:
     return make_args(x=inp.xs[rank], out=outs.out[local], rows=cfg.rows, mode=mode, algo=cfg.algo, input=cfg.input,
                      epilogue=cfg.epilogue, gs=inp.gs, res_in=inp.res, res_out=outs.res_out[local], weight=inp.weight,
-                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags, variant=cfg.variant)
+                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags, variant=cfg.variant,
+                     team_warps=cfg.team_warps)
 
 
 def _mism(t: Optional[torch.Tensor], want: Optional[np.ndarray]) -> int:
