@@ -138,8 +138,8 @@ def main(argv=None) -> int:
                                 emit({**common, "variant": "fp4ar", "mode": mode, "algo": algo, "rows": rows,
                                       "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags, "kernel_variant": ns.variant,
                                       "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
-                                      "p90_us": round(t["p90_us"], 3), "sm_mhz": c.get("sm_mhz"),
-                                      "reasons": c.get("reasons"), "status": st.describe(),
+                                      "p90_us": round(t["p90_us"], 3), "rank_med_us": t.get("rank_med_us"),
+                                      "sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons"), "status": st.describe(),
                                       "wire_gbs": round(rows * 3460 * (1 if world <= 2 else 2 * (world - 1) / world) /
                                                         t["med_us"] / 1e3, 1) if world > 1 else None})
                             if all(k in res for k in ("fused", "xport", "compute", "empty")):

@@ -63,10 +63,18 @@ def time_replays(graph: torch.cuda.CUDAGraph, calls: int, iters: int, warmup: in
     torch.cuda.synchronize(device)
     ms = torch.tensor([a.elapsed_time(b) for a, b in ev], dtype=torch.float64, device=device)
     d = _dist()
+    rank_med = [float(ms.median().item()) * 1000.0 / calls]           # this rank's own median, before the max over ranks
     if d is not None and d.get_world_size() > 1:
+        try:
+            mine = torch.tensor(rank_med, dtype=torch.float64, device=device)
+            every = [torch.zeros_like(mine) for _ in range(d.get_world_size())]
+            d.all_gather(every, mine)
+            rank_med = [float(t.item()) for t in every]
+        except Exception:        # the per-rank view is informational: never lose a measurement over it
+            pass
         d.all_reduce(ms, op=d.ReduceOp.MAX)
     us = sorted((ms * 1000.0 / calls).tolist())
     n = len(us)
     return {"med_us": statistics.median(us), "p10_us": us[max(0, int(0.1 * n))], "p90_us": us[min(n - 1, int(0.9 * n))],
             "min_us": us[0], "iters": iters, "warmup": warmup, "calls_per_graph": calls,
-            "total_ms": float(ms.sum().item())}
+            "total_ms": float(ms.sum().item()), "rank_med_us": [round(v, 3) for v in rank_med]}
