@@ -61,6 +61,12 @@ struct ArParams {
   unsigned long long* phase_cycles;   // tuning builds only (-DFP4AR_PHASE_TIMERS): 16 per-phase cycle counters
 };
 
+// Teams per CTA of the six-warp shapes: 3 (18 warps, 112 registers available) unless an experimental translation
+// unit asks for 4 (24 warps, 85 registers); such a unit must also rename the kernel (FP4AR_KERNEL_NAME).
+#ifndef FP4AR_T6_TEAMS
+#define FP4AR_T6_TEAMS 3
+#endif
+
 template <int P, int ALGO, int IN, int EPI, int T>
 struct ArShape {
   static constexpr int NJ = 6 / T;                                   // pairs per lane per row
@@ -82,7 +88,7 @@ struct ArShape {
   // residual: those shapes get fewer, fatter threads.
   // (Register budget per thread = 65536 / (32 * T * kMaxTeams).)
   static constexpr int kHeavy = (ALGO == 1 || EPI > 0) ? 1 : 0;
-  static constexpr int kMaxTeams = T == 2 ? (kHeavy ? 6 : 8) : (T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : 3));
+  static constexpr int kMaxTeams = T == 2 ? (kHeavy ? 6 : 8) : (T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : FP4AR_T6_TEAMS));
   static __host__ __device__ constexpr int smem_bytes(int teams) { return teams * kTeamBytes + kCtaExtra; }
 };
 

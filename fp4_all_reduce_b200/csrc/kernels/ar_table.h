@@ -39,6 +39,7 @@ void ar_register_p8(ArKernelEntry* out, int* n);
 void ar_register_p8b(ArKernelEntry* out, int* n);
 void ar_register_cmp(ArKernelEntry* out, int* n);
 void ar_register_t6(ArKernelEntry* out, int* n);     // six-warp teams, two-shot shapes of 4 and 8 ranks (ar_inst_t6.cu)
+void ar_register_t6x4(ArKernelEntry* out, int* n);   // variant 2: six-warp teams, four teams per CTA (ar_inst_t6x4.cu)
 void ar_register_cold(ArKernelEntry* out, int* n);   // variant 1: slow poll paths out of line (ar_inst_cold.cu)
 
 }  // namespace fp4ar

@@ -66,6 +66,7 @@ static std::vector<ArKernelEntry>& kernel_table() {
     ar_register_p4(buf, &n); ar_register_p4b(buf, &n); ar_register_p8(buf, &n); ar_register_p8b(buf, &n);
     ar_register_cmp(buf, &n);
     ar_register_t6(buf, &n);
+    ar_register_t6x4(buf, &n);
     ar_register_cold(buf, &n);
     table.assign(buf, buf + n);
   });
