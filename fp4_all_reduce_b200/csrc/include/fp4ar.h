@@ -113,6 +113,8 @@ int fp4ar_get_push_view(fp4ar_ctx* ctx, int local_rank, fp4ar_push_view* out);
 int fp4ar_ctas_per_rank(fp4ar_ctx* ctx);
 const char* fp4ar_last_cuda_error(void);
 const char* fp4ar_build_info(void);
+/* Teams per CTA of the compiled kernel for this shape (0 = not compiled).  variant 0 = product kernels. */
+int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps, int variant);
 
 /* ---- stand-alone codec / norm kernels (single GPU, no window) ---- */
 int fp4ar_encode(const void* x_bf16, int rows, void* values, long values_pitch, void* scales, long scales_pitch,

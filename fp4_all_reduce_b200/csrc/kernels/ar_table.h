@@ -18,8 +18,10 @@ struct ArKernelEntry {
 
 constexpr int kDefaultTeamWarps = 3;   // warps per row team unless a launch asks for another compiled width
 
+// Internal linkage on purpose: experimental translation units instantiate this template for shapes that a product unit
+// also instantiates, with a different kernel behind it; every unit must keep its own copy.
 template <int P, int ALGO, int IN, int EPI, int T>
-inline ArKernelEntry make_entry() {
+static inline ArKernelEntry make_entry() {
   using S = ArShape<P, ALGO, IN, EPI, T>;
   ArKernelEntry e;
   e.P = P; e.algo = ALGO; e.input = IN; e.epi = EPI; e.T = T;

@@ -250,6 +250,11 @@ extern "C" const char* fp4ar_last_cuda_error(void) {
   return copy.c_str();
 }
 
+extern "C" int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps, int variant) {
+  const ArKernelEntry* e = find_kernel(nranks, algo, input, epilogue, team_warps, variant);
+  return e && e->fn ? e->max_teams : 0;
+}
+
 extern "C" const char* fp4ar_build_info(void) {
   static std::string s;
   if (s.empty()) {
