@@ -65,7 +65,8 @@ typedef struct fp4ar_args {
   int tune[4];            /* [0] teams per CTA (0 = default), [1] bit 0: no programmatic dependent launch, bits 8-15: experimental kernel build
                              (0 = product kernels; 1 = slow poll paths out of line; 2 = six-warp teams x 4 per CTA, with [2] = 6;
                              both for the two-shot shapes of 4 and 8 ranks only),
-                             [2] warps per row team (0 = default 3; compiled widths: 2, 3, and 6 for the two-shot shapes of 4 and 8 ranks),
+                             [2] warps per row team (0 = default 3; compiled widths: 2, 3, and 6 for the default algorithm of each degree with
+                             no or BF16-norm epilogue),
                              [3] two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default) */
 } fp4ar_args;
 

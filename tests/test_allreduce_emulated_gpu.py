@@ -133,7 +133,7 @@ def test_experimental_build_with_cold_paths_is_bit_identical(P, inp, epi):
 
 @pytest.mark.skipif(__import__("os").environ.get("FP4AR_RUN_UNVERIFIED") != "1",
                     reason="six-warp teams, first GPU run pending; set FP4AR_RUN_UNVERIFIED=1")
-@pytest.mark.parametrize("P", [4, 8])
+@pytest.mark.parametrize("P", [1, 2, 4, 8])
 @pytest.mark.parametrize("inp,epi", [(N.IN_BF16, 0), (N.IN_BF16, 1), (N.IN_NVFP4, 0), (N.IN_NVFP4, 1)])
 def test_six_warp_teams_are_bit_identical(P, inp, epi):
     rec = gate_cell_emulated(CellConfig(nranks=P, rows=700, input=inp, epilogue=epi, team_warps=6), reps=6, graph_calls=3,

@@ -70,4 +70,5 @@ def test_kernel_table_holds_every_product_shape_and_the_selectable_builds():
             assert has(P, 1, inp, epi, 3, 1) > 0           # experimental build 1 (cold paths)
             assert has(P, 1, inp, epi, 6, 2) == 4          # experimental build 2: four six-warp teams
             assert has(P, 1, inp, epi, 3, 0) == 4          # ... and the product kernel is still the one at variant 0
-    assert has(2, 0, 0, 0, 6, 0) == 0 and has(4, 1, 0, 0, 3, 7) == 0
+    assert has(1, 0, 0, 1, 6, 0) == 3 and has(2, 0, 0, 1, 6, 0) == 3 and has(2, 0, 2, 1, 6, 0) == 3
+    assert has(2, 1, 0, 0, 6, 0) == 0 and has(4, 1, 0, 0, 3, 7) == 0
