@@ -279,6 +279,8 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (algo != FP4AR_ALGO_ONESHOT && algo != FP4AR_ALGO_TWOSHOT) return FP4AR_ERR_ARGUMENT;
   if (c->nranks == 1) algo = FP4AR_ALGO_ONESHOT;
   const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, team_warps_for(a0));
+  // a team width that comes from the environment is a preference: shapes not compiled at that width use the default
+  if (!ke && a0.tune[2] <= 0) ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, kDefaultTeamWarps);
   if (!ke) return FP4AR_ERR_UNSUPPORTED;
   if (const int variant = kernel_variant_for(a0)) {
     const ArKernelEntry* kv = find_kernel(c->nranks, algo, a0.input, a0.epilogue, ke->T, variant);
