@@ -25,3 +25,20 @@ def pytest_collection_modifyitems(config, items):
             it.add_marker(pytest.mark.skip(reason="no CUDA device"))
         if "multigpu" in it.keywords and ndev < 2:
             it.add_marker(pytest.mark.skip(reason="needs >= 2 CUDA devices"))
+
+
+@pytest.fixture(scope="session")
+def cuda_lib():
+    """The CUDA library for tests that only call its HOST functions (no GPU needed): built in tree on first use,
+    skipped where there is no nvcc."""
+    import shutil
+
+    from fp4_all_reduce_b200 import _native as N
+    from fp4_all_reduce_b200 import build as B
+
+    if not N.cuda_library_path().exists():
+        if shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"):
+            pytest.skip("libfp4ar.so is not built and there is no nvcc to build it")
+        B.build_cuda()
+        N.cuda.cache_clear()
+    return N.cuda()

@@ -30,8 +30,8 @@ def test_unknown_context_id_is_an_error():
         A._ctx(987654)
 
 
-def test_window_bytes_and_argument_validation_without_a_gpu():
-    lib = N.cuda()
+def test_window_bytes_and_argument_validation_without_a_gpu(cuda_lib):
+    lib = cuda_lib
     assert lib.fp4ar_window_bytes(16384, 6144, 2) == 2 * 2 * 16384 * 3584   # 2 buffers x 2 sources x rows x slot
     assert lib.fp4ar_window_bytes(16384, 6144, 8) % (2 << 20) == 0
     assert lib.fp4ar_window_bytes(16384, 4096, 2) == 0      # only hidden 6144
@@ -47,12 +47,12 @@ def test_window_bytes_and_argument_validation_without_a_gpu():
     assert b"sm_100a" in lib.fp4ar_build_info()
 
 
-def test_kernel_table_holds_every_product_shape_and_the_selectable_builds():
+def test_kernel_table_holds_every_product_shape_and_the_selectable_builds(cuda_lib):
     """Host-side check of the compiled-shape table (no GPU): every product shape is registered under variant 0, and
     the selectable builds sit beside them without displacing them."""
     from fp4_all_reduce_b200 import _native as N
 
-    lib = N.cuda()
+    lib = cuda_lib
     has = lambda *a: int(lib.fp4ar_has_kernel(*a))
     for T in (2, 3):
         for P, algos in ((1, (0,)), (2, (0, 1)), (4, (0, 1)), (8, (0, 1))):

@@ -229,14 +229,14 @@ def test_benchmark_config0_two_simulated_ranks():
     assert rel < rel2 < 0.3
 
 
-def test_software_models_of_the_device_selftests_match_the_host_model():
+def test_software_models_of_the_device_selftests_match_the_host_model(cuda_lib):
     """The plain software encoders / decoders that the exhaustive GPU self-tests compare the hardware with
     (csrc/kernels/selftest.cu) agree with the host model on dense sweeps, so a GPU mismatch would point at the GPU side."""
     import ctypes as C
 
     from fp4_all_reduce_b200 import _native as NN
 
-    lib = NN.cuda()          # loading the library needs no GPU; only host functions are called
+    lib = cuda_lib           # loading the library needs no GPU; only host functions are called
     lib.fp4ar_selftest_soft_model.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     rng = np.random.default_rng(5)
     # E4M3: every BF16-representable non-negative value, a dense log sweep, ties, the saturation edge, inf and NaN
