@@ -10,6 +10,8 @@ implementations, and recordable in CUDA graphs (a launch has no host-side per-ca
     yq = torch.ops.fp4ar.all_reduce_add_rms_norm_quant(x, residual, weight, 1e-6, 1.0, 2, qscale, ctx_id)
     y = torch.ops.fp4ar.all_reduce_nvfp4(xq, gs, ctx_id)                                   # producer already emitted NVFP4
     y = torch.ops.fp4ar.all_reduce_add_rms_norm_nvfp4(xq, gs, residual, weight, 1e-6, 1.0, ctx_id)
+    y = torch.ops.fp4ar.linear_all_reduce_add_rms_norm(x, wt, gs, residual, weight, 1e-6, 1.0, ctx_id)   # row-parallel linear:
+                                                           # tcgen05 GEMM pushing NVFP4 partials into the peers + AllReduce + norm
 
 This is the op surface the reference project only plans (docs/INTEGRATION.md:18-23).
 """
@@ -54,6 +56,9 @@ _lib.define("encode(Tensor x) -> (Tensor, Tensor)")
 _lib.define("encode_static(Tensor x, float gs) -> Tensor")
 _lib.define("decode_sum(Tensor[] qrows, Tensor[] row_scales) -> Tensor")
 _lib.define("add_rms_norm(Tensor x, Tensor(a!) residual, Tensor weight, float eps, float weight_bias) -> Tensor")
+_lib.define("linear_nvfp4(Tensor x, Tensor wt, float gs) -> Tensor")
+_lib.define("linear_all_reduce_add_rms_norm(Tensor x, Tensor wt, float[] gs, Tensor(a!) residual, Tensor weight, float eps, "
+            "float weight_bias, int ctx) -> Tensor")
 
 
 def _all_reduce(x, ctx):
@@ -87,6 +92,19 @@ def _add_rms_norm(x, residual, weight, eps, weight_bias):
     return y
 
 
+def _linear_nvfp4(x, wt, gs):
+    from . import gemm as _gemm
+
+    return _gemm.gemm_nvfp4(x, wt, gs)
+
+
+def _linear_ar_norm(x, wt, gs, residual, weight, eps, weight_bias, ctx):
+    from . import gemm as _gemm
+
+    y, _ = _gemm.gemm_all_reduce_add_rms_norm(_ctx(ctx), x, wt, list(gs), residual, weight, eps=eps, weight_bias=weight_bias)
+    return y
+
+
 _lib.impl("all_reduce", _all_reduce, "CUDA")
 _lib.impl("all_reduce_nvfp4", _all_reduce_nvfp4, "CUDA")
 _lib.impl("all_reduce_add_rms_norm", _ar_norm, "CUDA")
@@ -96,6 +114,8 @@ _lib.impl("encode", lambda x: _codec.encode(x), "CUDA")
 _lib.impl("encode_static", lambda x, gs: _codec.encode_static(x, gs), "CUDA")
 _lib.impl("decode_sum", lambda q, r: _codec.decode_sum(list(q), list(r)), "CUDA")
 _lib.impl("add_rms_norm", _add_rms_norm, "CUDA")
+_lib.impl("linear_nvfp4", _linear_nvfp4, "CUDA")
+_lib.impl("linear_all_reduce_add_rms_norm", _linear_ar_norm, "CUDA")
 
 
 def _bf16_rows(t):
@@ -141,6 +161,17 @@ def _(x, gs):
 @torch.library.register_fake("fp4ar::decode_sum")
 def _(qrows, row_scales):
     return _bf16_rows(qrows[0])
+
+
+@torch.library.register_fake("fp4ar::linear_nvfp4")
+def _(x, wt, gs):
+    n = wt.shape[0]
+    return x.new_empty((x.shape[0], n // 2 + n // 16), dtype=torch.uint8)
+
+
+@torch.library.register_fake("fp4ar::linear_all_reduce_add_rms_norm")
+def _(x, wt, gs, residual, weight, eps, weight_bias, ctx):
+    return x.new_empty((x.shape[0], wt.shape[0]), dtype=torch.bfloat16)
 
 
 @torch.library.register_fake("fp4ar::add_rms_norm")

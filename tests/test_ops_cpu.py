@@ -23,6 +23,11 @@ def test_fake_impls_give_shapes_without_a_gpu():
         q, rs = torch.ops.fp4ar.encode(x)
         assert q.shape == (37, 3456) and rs.shape == (37,)
         assert torch.ops.fp4ar.decode_sum([q, q], [rs, rs]).shape == (37, 6144)
+        xk = torch.empty(37, 2048, dtype=torch.bfloat16)
+        wt = torch.empty(6144, 2048, dtype=torch.bfloat16)
+        assert torch.ops.fp4ar.linear_nvfp4(xk, wt, 0.5).shape == (37, 3456)
+        y = torch.ops.fp4ar.linear_all_reduce_add_rms_norm(xk, wt, [0.5, 0.5], res, w, 1e-6, 1.0, 1)
+        assert y.shape == (37, 6144) and y.dtype == torch.bfloat16
 
 
 def test_unknown_context_id_is_an_error():
