@@ -137,10 +137,17 @@ def cuda() -> C.CDLL:
     return lib
 
 
+class ContextPoisoned(RuntimeError):
+    """A device-side wait of an earlier call gave up; the context refuses launches until its collective `reset()`."""
+
+
 def check(rc: int, what: str) -> None:
     """Raise on a non-zero return code of the CUDA library."""
     if rc == 0:
         return
+    if rc == 4:
+        raise ContextPoisoned(f"{what} refused: an earlier call timed out waiting for a peer; read status(), then "
+                              "call reset() on every rank")
     detail = ""
     if rc == 3:
         detail = ": " + (cuda().fp4ar_last_cuda_error() or b"").decode()

@@ -34,6 +34,7 @@ struct StatusWords {
 struct WaitCtx {
   StatusWords* status;            // global memory
   volatile uint32_t* cta_abort;   // shared memory flag of this CTA
+  uint32_t* host_poison;          // device-mapped host word the launch path reads without a sync (may be null)
   unsigned long long limit_ns;    // how long one wait may last
   uint32_t cta, call;
 };
@@ -52,6 +53,10 @@ static __device__ __noinline__ void report_wait_failure(const WaitCtx& w, uint32
     w.status->cta = w.cta; w.status->call = w.call;
   }
   atomicAdd(&w.status->count, 1u);
+  if (w.host_poison) {
+    *reinterpret_cast<volatile uint32_t*>(w.host_poison) = code;
+    __threadfence_system();
+  }
 }
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -19,7 +19,10 @@
  *    library, until the process exits.
  *  - The function calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on a
  *    device looks up the array's device address (cudaGetSymbolAddress) and raises the kernel's shared-memory
- *    limit; make that first call with the device current and before any stream capture begins.
+ *    limit; make that first call with the device current and before any stream capture begins.  Later calls
+ *    on that device take no lock and make no CUDA call other than cudaGetDevice, the launch and cudaGetLastError.  The address
+ *    and the raised limit are remembered per device for the life of the process: after cudaDeviceReset() on
+ *    a device they are stale, and this entry point must not be used on that device again.
  *  - Every call on a device shares the one array, which keeps the previous call's records.  Nothing in it has
  *    to start at zero (each call overwrites every byte it later reads), but two calls that overlap on the
  *    GPU -- different streams, or different host threads -- race on it: serialise them.

@@ -45,6 +45,7 @@ struct RankIO {
   char* win[kMaxRanks];
   uint32_t* ctrl;        // per-CTA call counters
   StatusWords* status;
+  uint32_t* poison;      // device-mapped host word: non-zero after a wait gave up (read by the launch path)
   int rank;
   int pad;
 };
@@ -246,7 +247,7 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   pdl_release_dependents();
 
   WaitCtx wctx;
-  wctx.status = io.status; wctx.cta_abort = abort_flag; wctx.limit_ns = prm.timeout_ns;
+  wctx.status = io.status; wctx.cta_abort = abort_flag; wctx.host_poison = io.poison; wctx.limit_ns = prm.timeout_ns;
   wctx.cta = (uint32_t)cta; wctx.call = call;
 
   const size_t buf_off = (size_t)(call & 1u) * prm.buf_bytes;

@@ -9,6 +9,8 @@
 //
 // Reference project counterparts: bench/codec/codec_bench.cu:139-590 (k_enc_*, k_dec_*, k_ts_*),
 // kernels/push/tp2_l2.cu:967-978 (fill_sentinel), bench/fused_norm/drv_norm.cu:75-123 (ref_norm).
+#include <atomic>
+#include <mutex>
 #include "../include/fp4ar.h"
 #include "../include/fp4ar_codec.cuh"
 #include "../include/fp4ar_async.cuh"
@@ -269,15 +271,22 @@ __global__ void fill_sentinel_kernel(uint4* win, size_t buf_units, int nbuf) {
 }
 
 // A word the kernels above set when a local row load did not arrive in time.
+// One word per device for the whole process (allocated on the first use on that device, never freed).
 static uint32_t* ops_error_word() {
-  static thread_local uint32_t* p[64] = {nullptr};
+  static std::mutex mu;
+  static std::atomic<uint32_t*> p[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!p[dev]) {
-    if (cudaMalloc(&p[dev], 16) != cudaSuccess) return nullptr;
-    cudaMemset(p[dev], 0, 16);
+  uint32_t* w = p[dev].load(std::memory_order_acquire);
+  if (w) return w;
+  std::lock_guard<std::mutex> lock(mu);
+  w = p[dev].load(std::memory_order_acquire);
+  if (!w) {
+    if (cudaMalloc(&w, 16) != cudaSuccess) return nullptr;
+    cudaMemset(w, 0, 16);
+    p[dev].store(w, std::memory_order_release);
   }
-  return p[dev];
+  return w;
 }
 
 static int ops_grid(int rows) {
@@ -286,9 +295,31 @@ static int ops_grid(int rows) {
   return need < sms ? (need > 0 ? need : 1) : sms;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device); later calls are two atomic loads.
+// (Every kernel of this file is launched with the one size kOpsSmem.)
+struct SmemRaised {
+  std::atomic<const void*> fn{nullptr};
+  std::atomic<unsigned long long> devices{0};   // bit d: done on device d
+};
+static SmemRaised g_smem_raised[64];
 template <class K>
 static bool ensure_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  const void* key = reinterpret_cast<const void*>(kernel);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  SmemRaised* slot = nullptr;
+  for (SmemRaised& e : g_smem_raised) {
+    const void* cur = e.fn.load(std::memory_order_acquire);
+    if (cur == nullptr) {
+      const void* expected = nullptr;
+      if (e.fn.compare_exchange_strong(expected, key, std::memory_order_acq_rel)) cur = key; else cur = expected;
+    }
+    if (cur == key) { slot = &e; break; }
+  }
+  if (slot && dev >= 0 && dev < 64 && ((slot->devices.load(std::memory_order_acquire) >> dev) & 1ull)) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (slot && dev >= 0 && dev < 64) slot->devices.fetch_or(1ull << dev, std::memory_order_release);
+  return true;
 }
 
 }  // namespace fp4ar
@@ -436,22 +467,25 @@ static int noalloc_fail(int code, const char* text) {
 }
 
 // Device address of the array on the current device; looked up once per device, with that device current.
+// After the first call on a device this is one atomic load: no lock, no CUDA call besides cudaGetDevice.
 static void* noalloc_records_on_current_device() {
   static std::mutex mu;
-  static void* addr[64] = {nullptr};
+  static std::atomic<void*> addr[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (p) return p;
   std::lock_guard<std::mutex> lock(mu);
-  if (!addr[dev]) {
-    void* p = nullptr;
+  p = addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_records);
     if (e != cudaSuccess || !p) {
       fp4ar::set_last_cuda_error(e, "cudaGetSymbolAddress(g_noalloc_records)");
       return nullptr;
     }
-    addr[dev] = p;
+    addr[dev].store(p, std::memory_order_release);
   }
-  return addr[dev];
+  return p;
 }
 
 extern "C" const char* fp4ar_noalloc_last_error(void) { return g_noalloc_error; }

@@ -8,9 +8,12 @@
 // one-shot, two-shot and NVFP4-input regions).
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 #include "../include/fp4ar.h"
 #include "../kernels/ar_table.h"
@@ -36,15 +39,15 @@ int cuda_check_launch() {
   return FP4AR_ERR_CUDA;
 }
 int device_sm_count() {
-  static int cache[64] = {0};
+  static std::atomic<int> cache[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
-  if (!cache[dev]) {
-    int n = 0;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (!n) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
-    cache[dev] = n;
+    cache[dev].store(n, std::memory_order_relaxed);   // every thread computes the same value
   }
-  return cache[dev];
+  return n;
 }
 
 #define FP4AR_CUDA(call)                                    \
@@ -127,17 +130,32 @@ static Geometry geometry(int max_rows, int nranks) {
 using namespace fp4ar;
 
 struct fp4ar_ctx {
-  int rank, nranks, device, max_rows;
-  int nlocal;            // ranks run by one launch (1, or nranks when emulated)
-  bool emulated;
-  int ctas_per_rank;
-  Geometry geo;
-  size_t window_bytes;
-  char* win[FP4AR_MAX_RANKS];
-  uint32_t* ctrl[FP4AR_MAX_RANKS];
-  StatusWords* status[FP4AR_MAX_RANKS];
-  unsigned long long timeout_ns;
-  int max_smem_optin;
+  int rank = 0, nranks = 0, device = 0, max_rows = 0;
+  int nlocal = 0;        // ranks run by one launch (1, or nranks when emulated)
+  bool emulated = false;
+  int ctas_per_rank = 0;
+  Geometry geo{};
+  size_t window_bytes = 0;
+  char* win[FP4AR_MAX_RANKS] = {};
+  uint32_t* ctrl[FP4AR_MAX_RANKS] = {};
+  StatusWords* status[FP4AR_MAX_RANKS] = {};
+  // One word of pinned, device-mapped host memory: a wait that gives up stores its status code here, and
+  // fp4ar_launch reads it on the host (no synchronisation) to refuse further calls until fp4ar_reset.
+  uint32_t* poison_host = nullptr;
+  uint32_t* poison_dev = nullptr;
+  unsigned long long timeout_ns = 0;
+  int max_smem_optin = 0;
+  // kernels whose dynamic shared-memory limit this context has already raised (function, bytes)
+  std::vector<std::pair<const void*, int>> smem_raised;
+  std::mutex mu;
+
+  ~fp4ar_ctx() {
+    for (int l = 0; l < FP4AR_MAX_RANKS; l++) {
+      if (ctrl[l]) cudaFree(ctrl[l]);
+      if (status[l]) cudaFree(status[l]);
+    }
+    if (poison_host) cudaFreeHost(poison_host);
+  }
 };
 
 extern "C" size_t fp4ar_window_bytes(int max_rows, int hidden, int nranks) {
@@ -155,8 +173,7 @@ static int create_common(fp4ar_ctx** out, int rank, int nranks, int device, int 
   for (int r = 0; r < nranks; r++)
     if (!windows[r] || ((uintptr_t)windows[r] & 255)) return FP4AR_ERR_ARGUMENT;
   FP4AR_CUDA(cudaSetDevice(device));
-  fp4ar_ctx* c = new fp4ar_ctx();
-  std::memset(c, 0, sizeof(*c));
+  std::unique_ptr<fp4ar_ctx> c(new fp4ar_ctx());   // freed, with its device buffers, on every error return below
   c->rank = rank; c->nranks = nranks; c->device = device; c->max_rows = max_rows;
   c->emulated = emulated; c->nlocal = emulated ? nranks : 1;
   c->geo = geometry(max_rows, nranks);
@@ -167,7 +184,10 @@ static int create_common(fp4ar_ctx** out, int rank, int nranks, int device, int 
   FP4AR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
   FP4AR_CUDA(cudaDeviceGetAttribute(&c->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
   c->ctas_per_rank = emulated ? sms / nranks : sms;
-  if (c->ctas_per_rank < 1) { delete c; return FP4AR_ERR_UNSUPPORTED; }
+  if (c->ctas_per_rank < 1) return FP4AR_ERR_UNSUPPORTED;
+  FP4AR_CUDA(cudaHostAlloc((void**)&c->poison_host, 64, cudaHostAllocMapped));
+  *c->poison_host = 0u;
+  FP4AR_CUDA(cudaHostGetDevicePointer((void**)&c->poison_dev, c->poison_host, 0));
   for (int l = 0; l < c->nlocal; l++) {
     FP4AR_CUDA(cudaMalloc(&c->ctrl[l], sizeof(uint32_t) * c->ctas_per_rank));
     FP4AR_CUDA(cudaMemset(c->ctrl[l], 0, sizeof(uint32_t) * c->ctas_per_rank));
@@ -181,7 +201,7 @@ static int create_common(fp4ar_ctx** out, int rank, int nranks, int device, int 
     if (rc != FP4AR_OK) return rc;
   }
   FP4AR_CUDA(cudaDeviceSynchronize());
-  *out = c;
+  *out = c.release();
   return FP4AR_OK;
 }
 
@@ -196,10 +216,6 @@ extern "C" int fp4ar_create_emulated(fp4ar_ctx** ctx, int nranks, int device, in
 
 extern "C" int fp4ar_destroy(fp4ar_ctx* c) {
   if (!c) return FP4AR_ERR_ARGUMENT;
-  for (int l = 0; l < c->nlocal; l++) {
-    if (c->ctrl[l]) cudaFree(c->ctrl[l]);
-    if (c->status[l]) cudaFree(c->status[l]);
-  }
   delete c;
   return FP4AR_OK;
 }
@@ -228,6 +244,7 @@ extern "C" int fp4ar_reset(fp4ar_ctx* c) {
     FP4AR_CUDA(cudaMemset(c->ctrl[l], 0, sizeof(uint32_t) * c->ctas_per_rank));
   }
   FP4AR_CUDA(cudaDeviceSynchronize());
+  *reinterpret_cast<volatile uint32_t*>(c->poison_host) = 0u;
   return FP4AR_OK;
 }
 
@@ -274,6 +291,12 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (a0.hidden != FP4AR_HIDDEN || a0.rows < 0 || a0.rows > c->max_rows) return FP4AR_ERR_ARGUMENT;
   if (a0.mode < 0 || a0.mode > 2 || a0.input < 0 || a0.input > 2 || a0.epilogue < 0 || a0.epilogue > 3)
     return FP4AR_ERR_ARGUMENT;
+  // A wait of an earlier call gave up: some receive slots may still hold data or miss their re-arm, so every
+  // later result would be wrong.  The word is written by the device into mapped host memory; reading it costs
+  // no synchronisation (a call enqueued before the failing kernel ran cannot see it yet).
+  if (*reinterpret_cast<volatile uint32_t*>(c->poison_host) != 0u) return FP4AR_ERR_POISONED;
+  // Nothing to reduce: no launch, so the device call counter (and with it the buffer parity) does not move.
+  if (a0.rows == 0) return FP4AR_OK;
   int algo = a0.algo;
   if (algo == FP4AR_ALGO_AUTO) algo = c->nranks <= 2 ? FP4AR_ALGO_ONESHOT : FP4AR_ALGO_TWOSHOT;
   if (algo != FP4AR_ALGO_ONESHOT && algo != FP4AR_ALGO_TWOSHOT) return FP4AR_ERR_ARGUMENT;
@@ -311,7 +334,7 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
     io.x = (const char*)a.x; io.out = (char*)a.out;
     io.res_in = (const char*)a.res_in; io.res_out = (char*)a.res_out; io.outq = (char*)a.outq;
     for (int r = 0; r < c->nranks; r++) io.win[r] = c->win[r];
-    io.ctrl = c->ctrl[l]; io.status = c->status[l];
+    io.ctrl = c->ctrl[l]; io.status = c->status[l]; io.poison = c->poison_dev;
     io.rank = c->emulated ? l : c->rank;
   }
   prm.weight = (const char*)a0.weight;
@@ -352,7 +375,21 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (a0.tune[0] > 0 && a0.tune[0] < teams) teams = a0.tune[0];
   if (teams < 1) return FP4AR_ERR_UNSUPPORTED;
   const int smem = teams * ke->team_bytes + ke->cta_extra;
-  FP4AR_CUDA(cudaFuncSetAttribute(ke->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  {
+    // the limit is raised once per (context, kernel), not on every launch
+    std::lock_guard<std::mutex> lk(c->mu);
+    bool done = false;
+    for (auto& e : c->smem_raised)
+      if (e.first == ke->fn) {
+        if (e.second >= smem) done = true;
+        else { FP4AR_CUDA(cudaFuncSetAttribute(ke->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); e.second = smem; done = true; }
+        break;
+      }
+    if (!done) {
+      FP4AR_CUDA(cudaFuncSetAttribute(ke->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      c->smem_raised.emplace_back(ke->fn, smem);
+    }
+  }
 
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));

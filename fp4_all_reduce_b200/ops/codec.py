@@ -18,15 +18,21 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _req(t: torch.Tensor, dtype, cols: int | None, name: str) -> torch.Tensor:
-    if not t.is_cuda:
-        raise ValueError(f"{name} must be a CUDA tensor")
+def _req_layout(t: torch.Tensor, dtype, cols: int | None, name: str) -> torch.Tensor:
+    """dtype, shape [rows, cols] and contiguity; the device is the caller's business."""
     if t.dtype != dtype:
         raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
     if cols is not None and (t.dim() != 2 or t.shape[1] != cols):
         raise ValueError(f"{name} must have shape [rows, {cols}], got {tuple(t.shape)}")
     if not t.is_contiguous():
         raise ValueError(f"{name} must be contiguous")
+    return t
+
+
+def _req(t: torch.Tensor, dtype, cols: int | None, name: str) -> torch.Tensor:
+    _req_layout(t, dtype, cols, name)
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
     return t
 
 

@@ -148,7 +148,9 @@ class Fp4ArContext(_Base):
         else:                      # no process group: a one-rank context (encode, decode of the own encoding, epilogue)
             self.group, self.rank, self.nranks = None, 0, 1
         self.max_rows = max_rows
-        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if device is None or device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
         lib = N.cuda()
         self.window_bytes = int(lib.fp4ar_window_bytes(max_rows, N.HIDDEN, self.nranks))
         if self.window_bytes == 0:
@@ -186,14 +188,46 @@ class Fp4ArContext(_Base):
         N.check(N.cuda().fp4ar_reset(self._ctx), "fp4ar_reset")
         self._barrier()
 
+    # ---- argument checks of the convenience wrappers (the kernel trusts its pointers) ----
+    def _check_input(self, x: torch.Tensor, gs) -> int:
+        """Returns the input kind after checking dtype, shape, contiguity, scales, row count and device."""
+        from ..ops.codec import _req_layout
+
+        if x.dtype == torch.bfloat16:
+            _req_layout(x, torch.bfloat16, N.HIDDEN, "x")
+            kind = N.IN_BF16
+        elif x.dtype == torch.uint8:
+            _req_layout(x, torch.uint8, N.QROW_BYTES, "x (NVFP4 rows)")
+            kind = N.IN_NVFP4
+            if gs is None or len(gs) != self.nranks or not all(float(g) > 0.0 for g in gs):
+                raise ValueError(f"NVFP4 input needs `gs`: one positive static scale per rank ({self.nranks})")
+        else:
+            raise ValueError(f"x must be bfloat16 [rows, {N.HIDDEN}] or uint8 NVFP4 rows [rows, {N.QROW_BYTES}], got {x.dtype}")
+        if x.shape[0] > self.max_rows:
+            raise ValueError(f"{x.shape[0]} rows exceed the context's max_rows {self.max_rows}")
+        if x.device != self.device:
+            raise ValueError(f"x is on {x.device}, the context on {self.device}")
+        return kind
+
+    def _check_like(self, t: torch.Tensor, dtype, rows: int, cols: int, name: str) -> None:
+        from ..ops.codec import _req_layout
+
+        _req_layout(t, dtype, cols, name)
+        if t.shape[0] != rows:
+            raise ValueError(f"{name} must have {rows} rows, got {t.shape[0]}")
+        if t.device != self.device:
+            raise ValueError(f"{name} is on {t.device}, the context on {self.device}")
+
     # ---- convenience wrappers: allocate outputs, launch on the current stream ----
     def all_reduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, *, gs=None, algo=N.ALGO_AUTO,
                    mode=N.MODE_FUSED, teams: int = 0) -> torch.Tensor:
         """x: BF16 [rows,6144] partial, or NVFP4 rows [rows,3456] uint8 with the static scales `gs`."""
-        kind = N.IN_BF16 if x.dtype == torch.bfloat16 else N.IN_NVFP4
+        kind = self._check_input(x, gs)
         rows = x.shape[0]
         if out is None:
             out = torch.empty(rows, N.HIDDEN, dtype=torch.bfloat16, device=x.device)
+        else:
+            self._check_like(out, torch.bfloat16, rows, N.HIDDEN, "out")
         self.launch(make_args(x=x, out=out, rows=rows, input=kind, gs=gs, algo=algo, mode=mode, teams=teams))
         return out
 
@@ -202,14 +236,26 @@ class Fp4ArContext(_Base):
                                 qscale: float = 1.0, gs=None, algo=N.ALGO_AUTO, out: Optional[torch.Tensor] = None,
                                 residual_out: Optional[torch.Tensor] = None, mode=N.MODE_FUSED, teams: int = 0):
         """Returns (normed output, updated residual).  `residual_out=None` updates `residual` in place."""
-        kind = N.IN_BF16 if x.dtype == torch.bfloat16 else N.IN_NVFP4
+        kind = self._check_input(x, gs)
         rows = x.shape[0]
+        if epilogue not in (N.EPI_NORM_BF16, N.EPI_NORM_NVFP4, N.EPI_NORM_MXFP8):
+            raise ValueError("epilogue must be 1 (BF16), 2 (NVFP4) or 3 (MXFP8)")
+        self._check_like(residual, torch.bfloat16, rows, N.HIDDEN, "residual")
+        if residual_out is not None:
+            self._check_like(residual_out, torch.bfloat16, rows, N.HIDDEN, "residual_out")
+        if (weight.device != self.device or weight.dtype != torch.bfloat16 or weight.numel() != N.HIDDEN
+                or not weight.is_contiguous()):
+            raise ValueError(f"weight must be a contiguous bfloat16 tensor of {N.HIDDEN} elements on {self.device}")
         res_out = residual if residual_out is None else residual_out
         o = q = None
         if epilogue == N.EPI_NORM_BF16:
+            if out is not None:
+                self._check_like(out, torch.bfloat16, rows, N.HIDDEN, "out")
             o = out if out is not None else torch.empty(rows, N.HIDDEN, dtype=torch.bfloat16, device=x.device)
         else:
             nb = N.QROW_BYTES if epilogue == N.EPI_NORM_NVFP4 else N.MXROW_BYTES
+            if out is not None:
+                self._check_like(out, torch.uint8, rows, nb, "out")
             q = out if out is not None else torch.empty(rows, nb, dtype=torch.uint8, device=x.device)
         self.launch(make_args(x=x, out=o, rows=rows, input=kind, gs=gs, algo=algo, epilogue=epilogue, res_in=residual,
                               res_out=res_out, weight=weight, eps=eps, weight_bias=weight_bias, outq=q, qscale=qscale,

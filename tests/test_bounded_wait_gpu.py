@@ -50,9 +50,16 @@ def test_missing_peer_times_out_with_a_status(nranks):
     # the CUDA context is alive and other work is still correct
     y = (torch.ones(1024, device="cuda:0") * 2).sum().item()
     assert y == 2048.0
+    # the context refuses further calls (its window is no longer consistent) until it is reset
+    assert lib.fp4ar_launch(ctx, args, None) == 4
+    with pytest.raises(N.ContextPoisoned):
+        N.check(lib.fp4ar_launch(ctx, args, None), "launch")
     N.check(lib.fp4ar_reset(ctx), "reset")
     N.check(lib.fp4ar_status(ctx, 0, C.byref(st)), "status")
     assert st.code == 0
+    # after the reset a launch is accepted again (zero rows: accepted without a kernel, the peer is still absent)
+    zero = (N.Args * 1)(make_args(x=x, out=out, rows=0))
+    assert lib.fp4ar_launch(ctx, zero, None) == 0
     lib.fp4ar_destroy(ctx)
     rec = gate_cell_emulated(CellConfig(nranks=2, rows=64), reps=3, graph_calls=0)
     assert rec["pass"], rec

@@ -77,3 +77,67 @@ def test_kernel_table_holds_every_product_shape_and_the_selectable_builds(cuda_l
             assert has(P, 1, inp, epi, 3, 0) == 4          # ... and the product kernel is still the one at variant 0
     assert has(1, 0, 0, 1, 6, 0) == 3 and has(2, 0, 0, 1, 6, 0) == 3 and has(2, 0, 2, 1, 6, 0) == 3
     assert has(2, 1, 0, 0, 6, 0) == 0 and has(4, 1, 0, 0, 3, 7) == 0
+
+
+def _unbound_context(nranks=2, max_rows=64):
+    """A context object with only the fields the argument checks read (no GPU, no native context)."""
+    from fp4_all_reduce_b200.parallel.context import Fp4ArContext
+
+    ctx = Fp4ArContext.__new__(Fp4ArContext)
+    ctx.nranks, ctx.max_rows, ctx.device, ctx._ctx = nranks, max_rows, torch.device("cuda", 0), None
+    return ctx
+
+
+def test_all_reduce_wrappers_reject_bad_tensors_before_any_launch():
+    """Wrong dtype, width, strides, row count, scales or device never reach the kernel, which trusts its pointers."""
+    ctx = _unbound_context()
+    good = torch.zeros(8, 6144, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="bfloat16"):
+        ctx.all_reduce(good.float())
+    with pytest.raises(ValueError, match="shape"):
+        ctx.all_reduce(torch.zeros(8, 4096, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="contiguous"):
+        ctx.all_reduce(torch.zeros(8, 2 * 6144, dtype=torch.bfloat16)[:, ::2])
+    with pytest.raises(ValueError, match="is on cpu"):
+        ctx.all_reduce(good)                                        # a host tensor, context on cuda:0
+    with pytest.raises(ValueError, match="shape"):
+        ctx.all_reduce(torch.zeros(8, 3000, dtype=torch.uint8), gs=[1.0, 1.0])
+    xq = torch.zeros(8, 3456, dtype=torch.uint8)
+    with pytest.raises(ValueError, match="gs"):
+        ctx.all_reduce(xq)                                          # NVFP4 rows without scales
+    with pytest.raises(ValueError, match="gs"):
+        ctx.all_reduce(xq, gs=[1.0])                                # one scale per rank
+    with pytest.raises(ValueError, match="gs"):
+        ctx.all_reduce(xq, gs=[1.0, 0.0])
+    with pytest.raises(ValueError, match="max_rows"):
+        ctx.all_reduce(torch.zeros(65, 6144, dtype=torch.bfloat16))
+
+
+def test_companion_tensors_of_the_norm_call_are_checked():
+    ctx = _unbound_context()
+    ctx.device = torch.device("cpu")            # host tensors pass the device test, so every later check is reached
+    x = torch.zeros(8, 6144, dtype=torch.bfloat16)
+    res = torch.zeros(8, 6144, dtype=torch.bfloat16)
+    w = torch.zeros(6144, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="epilogue"):
+        ctx.all_reduce_add_rms_norm(x, res, w, epilogue=7)
+    with pytest.raises(ValueError, match="residual must have 8 rows"):
+        ctx.all_reduce_add_rms_norm(x, res[:7], w)
+    with pytest.raises(ValueError, match="residual_out"):
+        ctx.all_reduce_add_rms_norm(x, res, w, residual_out=torch.zeros(8, 6000, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="weight"):
+        ctx.all_reduce_add_rms_norm(x, res, w[:100])
+    with pytest.raises(ValueError, match="weight"):
+        ctx.all_reduce_add_rms_norm(x, res, w.float())
+    with pytest.raises(ValueError, match="out must be"):
+        ctx.all_reduce_add_rms_norm(x, res, w, epilogue=2, out=torch.zeros(8, 3456, dtype=torch.int8))
+    with pytest.raises(ValueError, match="out must have shape"):
+        ctx.all_reduce_add_rms_norm(x, res, w, epilogue=3, out=torch.zeros(8, 3456, dtype=torch.uint8))
+    with pytest.raises(ValueError, match="out must have 8 rows"):
+        ctx.all_reduce(x, out=torch.zeros(9, 6144, dtype=torch.bfloat16))
+
+
+def test_zero_row_call_and_poisoned_code_have_names():
+    assert N.ERROR_NAMES[4] == "context poisoned"
+    with pytest.raises(N.ContextPoisoned):
+        N.check(4, "fp4ar_launch")
