@@ -20,6 +20,22 @@ HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 
 
+def reference_dir() -> str:
+    """Where the reference project's tree is: FP4AR_REFERENCE_DIR, else `reference_path` of BASELINE.json at the
+    repository root, else "" (nothing to build from)."""
+    import json
+    import os
+
+    d = os.environ.get("FP4AR_REFERENCE_DIR", "")
+    if d:
+        return d
+    try:
+        with open(HERE.parent / "BASELINE.json") as f:
+            return str(json.load(f).get("reference_path", ""))
+    except Exception:
+        return ""
+
+
 def nccl_paths():
     import nvidia
     base = Path(list(nvidia.__path__)[0]) / "nccl"
@@ -28,14 +44,14 @@ def nccl_paths():
 
 def copy_sources(ref: str) -> Path | None:
     src = OUT / "src"
-    if Path(ref).exists():
+    if ref and Path(ref).exists():
         if src.exists():
             shutil.rmtree(src)
         shutil.copytree(ref, src, ignore=shutil.ignore_patterns(".git"))
     return src if src.exists() else None
 
 
-def build_host_oracle(ref: str = "/root/reference", force: bool = False) -> Path | None:
+def build_host_oracle(ref: str | None = None, force: bool = False) -> Path | None:
     """baseline/_ref/libref_oracle.so: the reference's own CPU oracle (bench/codec/codec_bench.cu, `namespace cpu`)
     behind two C functions (baseline/ref_oracle_shim.cu).  Host code only runs; no GPU is needed to use it."""
     out = OUT / "libref_oracle.so"
@@ -43,7 +59,7 @@ def build_host_oracle(ref: str = "/root/reference", force: bool = False) -> Path
         return out
     src = OUT / "src"
     if not src.exists():
-        src = copy_sources(ref)
+        src = copy_sources(ref if ref is not None else reference_dir())
     if src is None:
         return None
     OUT.mkdir(exist_ok=True)
@@ -59,7 +75,7 @@ def build_host_oracle(ref: str = "/root/reference", force: bool = False) -> Path
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=reference_dir(), help="reference tree (default: FP4AR_REFERENCE_DIR or BASELINE.json)")
     ap.add_argument("--host-oracle", action="store_true", help="build only the CPU oracle bridge")
     ns = ap.parse_args(argv)
     if ns.host_oracle:

@@ -139,7 +139,11 @@ int fp4ar_selftest_scale_division(int exp_biased, unsigned long long* device_mis
 /* Exhaustive checks of the hardware conversions against plain software models; mismatches are added to the counter.
  * which 0: E4M3 block scale of x / 6 for the non-negative FP32 bit patterns [first, first + count) (domain 0 .. 2^31);
  * which 1: E2M1 value encode for the FP32 bit patterns [first, first + count) in every nibble position;
- * which 2: E2M1 / E4M3 decode tables and the -0 canonicalisation (first, count ignored).  count 0 = to the end. */
+ * which 2: E2M1 / E4M3 decode tables and the -0 canonicalisation (first, count ignored).  count 0 = to the end.
+ * which 3 / 4: `count` pseudo-random BF16 / FP32 pairs (seed `first`): the table-driven block encoder against the one
+ *          with IEEE divisions; counter[0] += mismatching words, counter[1] += sentinels produced (two counters);
+ * which 5: `count` (<= 2^17) rounds of 2^14 decode-accumulate cases, one per pair of non-negative scale bytes,
+ *          against scalar table arithmetic. */
 int fp4ar_selftest_conversions(int which, unsigned int first, unsigned int count,
                                unsigned long long* device_mismatch_counter, fp4ar_stream stream);
 

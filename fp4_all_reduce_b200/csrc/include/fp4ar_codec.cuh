@@ -123,7 +123,8 @@ __device__ __forceinline__ void e2m1_unpack8(uint32_t w, F2* out) {
   }
 }
 
-// Two non-negative floats -> two E4M3 bytes in the low 16 bits (first value in the low byte).
+// Two floats -> two E4M3 bytes in the low 16 bits (first value in the low byte).  Block scales feed it
+// non-negative numbers; the MXFP8 output feeds it signed ones.
 __device__ __forceinline__ uint32_t e4m3_pack2(float first, float second) {
   uint16_t r;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(second), "f"(first));
@@ -136,8 +137,6 @@ __device__ __forceinline__ F2 e4m3_unpack2(uint32_t two) {
   const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&h));
   F2 d; d.lo = t.x; d.hi = t.y; return d;
 }
-// Two floats -> two E4M3 bytes (signed values allowed; used by the MXFP8 output).
-__device__ __forceinline__ uint32_t e4m3_pack2_signed(float first, float second) { return e4m3_pack2(first, second); }
 
 // Map every -0 nibble (0x8) to +0 and leave all other nibbles alone.
 __device__ __forceinline__ uint32_t canon_neg0(uint32_t w) {
@@ -238,57 +237,33 @@ __device__ __forceinline__ uint32_t quant_chunk_bf16(uint4 c, float mult) {
   return CANON ? canon_neg0(w) : w;
 }
 
-// Encode a pair held as 32 BF16 (four 16 B chunks).  Returns the two scale bytes.
+// Eight floats (one 16-byte slot of a pair) times mult -> E2M1 word: the FP32 twin of quant_chunk_bf16.
 template <bool CANON>
-__device__ __forceinline__ uint32_t encode_pair_bf16(const uint4* c, float bm0, float bm1, float inv, uint4& q) {
-  float m0, m1;
-  const uint32_t sf2 = pair_block_scales(bm0, bm1, inv, m0, m1);
-  q.x = quant_chunk_bf16<CANON>(c[0], m0); q.y = quant_chunk_bf16<CANON>(c[1], m0);
-  q.z = quant_chunk_bf16<CANON>(c[2], m1); q.w = quant_chunk_bf16<CANON>(c[3], m1);
-  return sf2;
+__device__ __forceinline__ uint32_t quant_slot_f32(const float* v8, float mult) {
+  const F2 mm = f2_splat(mult);
+  F2 a, b, c, d;
+  a.lo = v8[0]; a.hi = v8[1]; b.lo = v8[2]; b.hi = v8[3]; c.lo = v8[4]; c.hi = v8[5]; d.lo = v8[6]; d.hi = v8[7];
+  const uint32_t w = e2m1_pack8(f2_mul(a, mm), f2_mul(b, mm), f2_mul(c, mm), f2_mul(d, mm));
+  return CANON ? canon_neg0(w) : w;
 }
-
-// Encode a pair held as 32 floats (an FP32 sum being re-encoded by the two-shot row owner).
-template <bool CANON>
-__device__ __forceinline__ uint32_t encode_pair_f32(const float* f, float inv, uint4& q) {
-  float bm0 = 0.0f, bm1 = 0.0f;
+__device__ __forceinline__ float absmax16(const float* f) {
+  float m = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; i++) { bm0 = fmaxf(bm0, fabsf(f[i])); bm1 = fmaxf(bm1, fabsf(f[16 + i])); }
-  float m0, m1;
-  const uint32_t sf2 = pair_block_scales(bm0, bm1, inv, m0, m1);
-  uint32_t w[4];
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    const F2 mm = f2_splat(k < 2 ? m0 : m1);
-    F2 g[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) { F2 v; v.lo = f[8 * k + 2 * i]; v.hi = f[8 * k + 2 * i + 1]; g[i] = f2_mul(v, mm); }
-    w[k] = e2m1_pack8(g[0], g[1], g[2], g[3]);
-    if (CANON) w[k] = canon_neg0(w[k]);
-  }
-  q = make_uint4(w[0], w[1], w[2], w[3]);
-  return sf2;
+  for (int i = 0; i < 16; i++) m = fmaxf(m, fabsf(f[i]));
+  return m;
 }
-
-// encode_pair_f32 with the table-based multipliers.
-template <bool CANON>
-__device__ __forceinline__ uint32_t encode_pair_f32_lut(const float* f, float inv, ScaleLut lut, bool exact_ok, uint4& q) {
-  float bm0 = 0.0f, bm1 = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; i++) { bm0 = fmaxf(bm0, fabsf(f[i])); bm1 = fmaxf(bm1, fabsf(f[16 + i])); }
-  float m0, m1;
-  const uint32_t sf2 = pair_block_scales_lut(bm0, bm1, inv, lut, exact_ok, m0, m1);
-  uint32_t w[4];
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    const F2 mm = f2_splat(k < 2 ? m0 : m1);
-    F2 g[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) { F2 v; v.lo = f[8 * k + 2 * i]; v.hi = f[8 * k + 2 * i + 1]; g[i] = f2_mul(v, mm); }
-    w[k] = e2m1_pack8(g[0], g[1], g[2], g[3]);
-    if (CANON) w[k] = canon_neg0(w[k]);
-  }
-  q = make_uint4(w[0], w[1], w[2], w[3]);
+// Encode a pair held as 32 floats (an FP32 sum re-encoded by the two-shot row owner, or a GEMM accumulator):
+// slots 0,1 are the first 16-value block, slots 2,3 the second.  `scales(bm0, bm1, mult0, mult1)` turns the two
+// block maxima into the scale bytes (returned) and the value multipliers: pair_block_scales with a row's
+// inverse scale, or its table-driven form.
+template <bool CANON, class Scales>
+__device__ __forceinline__ uint32_t encode_pair_f32(const float* f, Scales&& scales, uint4& q) {
+  float mult_a, mult_b;
+  const uint32_t sf2 = scales(absmax16(f), absmax16(f + 16), mult_a, mult_b);
+  q.x = quant_slot_f32<CANON>(f, mult_a);
+  q.y = quant_slot_f32<CANON>(f + 8, mult_a);
+  q.z = quant_slot_f32<CANON>(f + 16, mult_b);
+  q.w = quant_slot_f32<CANON>(f + 24, mult_b);
   return sf2;
 }
 
@@ -296,25 +271,6 @@ __device__ __forceinline__ float absmax32(const float* f, float m) {
 #pragma unroll
   for (int i = 0; i < 32; i++) m = fmaxf(m, fabsf(f[i]));
   return m;
-}
-
-// acc[i] = fma(e2m1(q_i), rn(e4m3(s_block) * rs), acc[i]) for the 32 values of one pair.
-__device__ __forceinline__ void decode_acc_pair(float* acc, uint4 q, uint32_t sf2, float rs) {
-  const F2 e = e4m3_unpack2(sf2);
-  const F2 s0 = f2_splat(__fmul_rn(e.lo, rs));
-  const F2 s1 = f2_splat(__fmul_rn(e.hi, rs));
-  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    F2 v[4];
-    e2m1_unpack8(w[k], v);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      F2 a; a.lo = acc[8 * k + 2 * i]; a.hi = acc[8 * k + 2 * i + 1];
-      a = f2_fma(v[i], k < 2 ? s0 : s1, a);
-      acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
-    }
-  }
 }
 
 __device__ __forceinline__ void zero32(float* acc) {
@@ -418,7 +374,7 @@ __device__ __forceinline__ uint32_t quant_pair_mxfp8_out(const uint4* yb, uint4*
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const F2 a = f2_mul(bf16x2_to_f2(yw[2 * i]), mm), b = f2_mul(bf16x2_to_f2(yw[2 * i + 1]), mm);
-    w[i] = e4m3_pack2_signed(a.lo, a.hi) | (e4m3_pack2_signed(b.lo, b.hi) << 16);
+    w[i] = e4m3_pack2(a.lo, a.hi) | (e4m3_pack2(b.lo, b.hi) << 16);
   }
   v[0] = make_uint4(w[0], w[1], w[2], w[3]);
   v[1] = make_uint4(w[4], w[5], w[6], w[7]);

@@ -18,11 +18,11 @@
  *  - The array (FP4AR_NOALLOC_MAX_ROWS x 3584 bytes, about 3.5 MiB) is resident on every GPU that loads the
  *    library, until the process exits.
  *  - The function calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on a
- *    device looks up the array's device address (cudaGetSymbolAddress) and raises the kernel's shared-memory
- *    limit; make that first call with the device current and before any stream capture begins.  Later calls
- *    on that device take no lock and make no CUDA call other than cudaGetDevice, the launch and cudaGetLastError.  The address
- *    and the raised limit are remembered per device for the life of the process: after cudaDeviceReset() on
- *    a device they are stale, and this entry point must not be used on that device again.
+ *    device looks up the array's device address (cudaGetSymbolAddress); make that first call with the device
+ *    current and before any stream capture begins.  Later calls on that device take no lock and make no CUDA
+ *    call other than cudaGetDevice, the launch and cudaGetLastError.  The address is remembered per device for
+ *    the life of the process: after cudaDeviceReset() on a device it is stale, and this entry point must not
+ *    be used on that device again.
  *  - Every call on a device shares the one array, which keeps the previous call's records.  Nothing in it has
  *    to start at zero (each call overwrites every byte it later reads), but two calls that overlap on the
  *    GPU -- different streams, or different host threads -- race on it: serialise them.

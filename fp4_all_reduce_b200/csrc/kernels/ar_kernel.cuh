@@ -596,7 +596,9 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
           for (int j = 0; j < NJ; j++) {
             const int p = lane + 32 * (tw + T * j);
             uint4 q;
-            uint32_t sf2 = encode_pair_f32_lut<true>(sums[j], sc.inv, slut, lut_ok, q);   // slot order
+            uint32_t sf2 = encode_pair_f32<true>(sums[j], [&](float b0, float b1, float& m0, float& m1) {
+              return pair_block_scales_lut(b0, b1, sc.inv, slut, lut_ok, m0, m1);
+            }, q);   // slot order
             lane_permute4(q.x, q.y, q.z, q.w, f);
             if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
             sts16(rec_own + 16 * p, q);

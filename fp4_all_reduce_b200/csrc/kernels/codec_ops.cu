@@ -3,9 +3,8 @@
 // owner step (decode-sum + re-encode + decode of the re-encoding), add + Gemma RMSNorm with BF16 /
 // NVFP4 / MXFP8 output, and the sentinel fill of a receive window.
 //
-// All of them stream 12 KB rows: one warp per row, rows brought into shared memory by bulk
-// asynchronous copies where the access pattern would otherwise be 64 B per lane, BF16 results staged
-// in shared memory and written back with one bulk store per row.
+// All of them stream 12 KB rows through teams of 192 threads (one pair of a row per thread, several teams per
+// SM); see "Row teams" below.
 //
 // Reference project counterparts: bench/codec/codec_bench.cu:139-590 (k_enc_*, k_dec_*, k_ts_*),
 // kernels/push/tp2_l2.cu:967-978 (fill_sentinel), bench/fused_norm/drv_norm.cu:75-123 (ref_norm).
@@ -19,43 +18,134 @@
 
 namespace fp4ar {
 
-// ---------------------------------------------------------------------------------------------
-// encode: x [rows][6144] BF16 -> values / scales / row scales
-// ---------------------------------------------------------------------------------------------
-template <bool STATIC>
-__global__ void __launch_bounds__(kOpsWarps * 32, 1)
-encode_rows_kernel(const char* __restrict__ x, int rows, char* values, long vpitch, char* scales, long spitch,
-                   float* row_scales, float inv_static, uint32_t* err) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  WarpSmem ws = carve(smem, warp);
-  if (lane == 0) { mbar_init(ws.bar, 1); mbar_init(ws.bar + 1, 1); }
-  mbar_init_fence();
+// =============================================================================================
+// Row teams.  Every kernel below gives a row to a team of 192 threads (6 warps): thread t owns pair t of the
+// row (values 32t .. 32t+31: 64 B of BF16, 16 B of E2M1, 2 scale bytes), so the compact NVFP4 fields are read
+// and written fully coalesced straight from registers.  The 64-byte BF16 pieces go through a 2 KB staging area
+// per warp: global memory is touched with consecutive 16-byte chunks per lane (512 B per warp instruction) and
+// the area is transposed into "own pair" order through a bank-conflict-free swizzle.  A CTA is one team; several
+// CTAs share an SM (the kernels need no more than 12.5 KB of shared memory and 64-112 registers), so the loads of
+// one team overlap the arithmetic of the others.  Teams walk rows with a grid stride and take U rows per trip,
+// issuing every load of the trip before the first use.
+// =============================================================================================
+constexpr int kTeamThreads = kPairs;          // 192
+constexpr int kTeamWarps = kTeamThreads / 32;  // 6
+constexpr int kStageBytes = 2048;              // per warp: 32 pairs x 64 B
+
+// chunk k (16 B) of lane l's pair inside the warp's staging area
+__device__ __forceinline__ int stage_off(int l, int k) { return l * 64 + ((k ^ ((l >> 1) & 3)) << 4); }
+
+// Global -> registers: the warp's 32 pairs (2 KB at `unit`) as four 16-byte chunks per lane, in chunk order.
+// load_issue() starts the coalesced loads; stage_in() transposes them through the staging area.
+__device__ __forceinline__ void load_issue(const char* unit, int lane, uint4* raw) {
+#pragma unroll
+  for (int it = 0; it < 4; it++) raw[it] = __ldcs(reinterpret_cast<const uint4*>(unit + (it * 32 + lane) * 16));
+}
+__device__ __forceinline__ void stage_in(uint8_t* stage, int lane, const uint4* raw, uint4* mine) {
   __syncwarp();
-  const int stride = gridDim.x * kOpsWarps;
-  int row = blockIdx.x * kOpsWarps + warp;
-  uint8_t* buf[2] = {ws.a, ws.b};
-  if (lane == 0 && row < rows) { mbar_arrive_expect(ws.bar, kRowB); bulk_load(buf[0], x + (size_t)row * kRowB, kRowB, ws.bar); }
-  for (int it = 0; row < rows; row += stride, it++) {
-    const int nxt = row + stride;
-    if (lane == 0 && nxt < rows) {
-      mbar_arrive_expect(ws.bar + ((it + 1) & 1), kRowB);
-      bulk_load(buf[(it + 1) & 1], x + (size_t)nxt * kRowB, kRowB, ws.bar + ((it + 1) & 1));
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int c = it * 32 + lane;
+    sts16(stage + stage_off(c >> 2, c & 3), raw[it]);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; k++) mine[k] = lds16(stage + stage_off(lane, k));
+}
+// Registers -> global: the reverse path.
+__device__ __forceinline__ void stage_out(uint8_t* stage, int lane, const uint4* mine, char* unit) {
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; k++) sts16(stage + stage_off(lane, k), mine[k]);
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int c = it * 32 + lane;
+    __stcs(reinterpret_cast<uint4*>(unit + c * 16), lds16(stage + stage_off(c >> 2, c & 3)));
+  }
+}
+
+// One float per warp -> the same six floats in every thread of the team (slot = parity of the exchange).
+__device__ __forceinline__ void team_exchange6(float* xchg, int& phase, int warp, int lane, float mine, float* all6) {
+  float* slot = xchg + 8 * (phase & 1);
+  phase++;
+  if (lane == 0) slot[warp] = mine;
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < kTeamWarps; g++) all6[g] = slot[g];
+}
+
+// acc (natural order) += decode of one pair of one source
+__device__ __forceinline__ void decode_acc_natural(float* acc, uint4 q, uint32_t sf2, float rs) {
+  const F2 e = e4m3_unpack2(sf2);
+  const F2 sa = f2_splat(__fmul_rn(e.lo, rs)), sb = f2_splat(__fmul_rn(e.hi, rs));
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    F2 v[4];
+    e2m1_unpack8(w[k], v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      F2 a; a.lo = acc[8 * k + 2 * i]; a.hi = acc[8 * k + 2 * i + 1];
+      a = f2_fma(v[i], k < 2 ? sa : sb, a);
+      acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
     }
-    wait_row(ws.bar + (it & 1), (uint32_t)((it >> 1) & 1), err);
-    char* vrow = values + (size_t)row * vpitch;
-    char* srow = scales + (size_t)row * spitch;
-    float rs;
-    encode_row_from_smem(buf[it & 1], lane, inv_static, STATIC, rs,
-                         [&](int p, uint4 q) { *reinterpret_cast<uint4*>(vrow + 16 * p) = q; },
-                         [&](int p, uint32_t sf2) { *reinterpret_cast<uint16_t*>(srow + 2 * p) = (uint16_t)sf2; });
-    if (!STATIC && lane == 0) row_scales[row] = rs;
-    __syncwarp();   // every lane is done with buf[it & 1] before it is refilled two iterations later
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// decode-sum: NS sources -> BF16 row; optional re-encode of the FP32 sum (two-shot owner step)
+// encode: x [rows][6144] BF16 -> values / scales / row scales
+// ---------------------------------------------------------------------------------------------
+template <bool STATIC>
+__global__ void __launch_bounds__(kTeamThreads, 4)
+encode_rows_kernel(const char* __restrict__ x, int rows, char* values, long vpitch, char* scales, long spitch,
+                   float* row_scales, float inv_static) {
+  __shared__ __align__(128) uint8_t stage_all[kTeamWarps * kStageBytes];
+  __shared__ float xchg[16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, p = threadIdx.x;
+  uint8_t* stage = stage_all + warp * kStageBytes;
+  int phase = 0;
+  constexpr int U = 2;
+  for (int row0 = blockIdx.x * U; row0 < rows; row0 += gridDim.x * U) {
+    uint4 raw[U][4];
+#pragma unroll
+    for (int u = 0; u < U; u++)
+      if (row0 + u < rows) load_issue(x + (size_t)(row0 + u) * kRowB + warp * kStageBytes, lane, raw[u]);
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int row = row0 + u;
+      if (row >= rows) break;           // uniform over the team
+      uint4 c[4];
+      stage_in(stage, lane, raw[u], c);
+      const __nv_bfloat162 z2 = __floats2bfloat162_rn(0.0f, 0.0f);
+      const uint32_t xa = bf16x2_hmax_bits(chunk_absmax(c[1], chunk_absmax(c[0], z2)));
+      const uint32_t xb = bf16x2_hmax_bits(chunk_absmax(c[3], chunk_absmax(c[2], z2)));
+      const float bm0 = __uint_as_float(xa << 16), bm1 = __uint_as_float(xb << 16);
+      float inv = inv_static, rs = 0.0f;
+      if (!STATIC) {
+        float g6[kTeamWarps];
+        team_exchange6(xchg, phase, warp, lane, warp_max(fmaxf(bm0, bm1)), g6);
+        float am = g6[0];
+#pragma unroll
+        for (int g = 1; g < kTeamWarps; g++) am = fmaxf(am, g6[g]);
+        const RowScale sc = row_scale_from_amax(am);
+        inv = sc.inv; rs = sc.rs;
+      }
+      float m0, m1;
+      const uint32_t sf2 = pair_block_scales(bm0, bm1, inv, m0, m1);
+      uint4 q;
+      q.x = quant_chunk_bf16<true>(c[0], m0); q.y = quant_chunk_bf16<true>(c[1], m0);
+      q.z = quant_chunk_bf16<true>(c[2], m1); q.w = quant_chunk_bf16<true>(c[3], m1);
+      __stcs(reinterpret_cast<uint4*>(values + (size_t)row * vpitch + 16 * p), q);
+      *reinterpret_cast<uint16_t*>(scales + (size_t)row * spitch + 2 * p) = (uint16_t)sf2;
+      if (!STATIC && p == 0) row_scales[row] = rs;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode-sum: NS sources -> BF16 row; optional re-encode of the FP32 sum (two-shot owner step): the sum is
+// decoded ONCE, kept in registers across the row-maximum exchange, re-encoded, and the re-encoding decoded.
 // ---------------------------------------------------------------------------------------------
 struct SrcList {
   const char* base[kMaxRanksOps];
@@ -64,194 +154,131 @@ struct SrcList {
 };
 
 template <int NS, bool REENC>
-__global__ void __launch_bounds__(kOpsWarps * 32, 1)
+__global__ void __launch_bounds__(kTeamThreads, (NS > 4 || REENC) ? 3 : 4)
 decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int f = (lane >> 1) & 3;
-  WarpSmem ws = carve(smem, warp);
-  const int stride = gridDim.x * kOpsWarps;
-  bool pending_store = false;
-  for (int row = blockIdx.x * kOpsWarps + warp; row < rows; row += stride) {
-    float rsv[NS];
+  __shared__ __align__(128) uint8_t stage_all[kTeamWarps * kStageBytes];
+  __shared__ float xchg[16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, p = threadIdx.x;
+  uint8_t* stage = stage_all + warp * kStageBytes;
+  int phase = 0;
+  constexpr int U = NS == 1 ? 4 : (NS == 2 ? 2 : 1);
+  for (int row0 = blockIdx.x * U; row0 < rows; row0 += gridDim.x * U) {
+    uint4 q[U][NS];
+    uint32_t sf[U][NS];
+    float rsv[U][NS];
 #pragma unroll
-    for (int s = 0; s < NS; s++) rsv[s] = src.rs[s] ? src.rs[s][row] : src.gs[s];
-    auto sum_pair = [&](int p, float* acc) {
-      zero32(acc);
+    for (int u = 0; u < U; u++) {
+      const int row = row0 + u < rows ? row0 + u : rows - 1;     // clamped: the extra loads are discarded
 #pragma unroll
       for (int s = 0; s < NS; s++) {
         const char* r = src.base[s] + (size_t)row * pitch;
-        uint4 q = __ldcg(reinterpret_cast<const uint4*>(r + 16 * p));
-        const uint32_t sf2 = __ldcg(reinterpret_cast<const unsigned short*>(r + kValueBytes + 2 * p));
-        perm4(q.x, q.y, q.z, q.w, f);
-        const F2 e = e4m3_unpack2(sf2);
-        const float s0 = __fmul_rn(e.lo, rsv[s]), s1 = __fmul_rn(e.hi, rsv[s]);
-        const F2 sa = f2_splat((f & 2) ? s1 : s0), sb = f2_splat((f & 2) ? s0 : s1);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-          F2 v[4];
-          e2m1_unpack8(w[k], v);
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            F2 a; a.lo = acc[8 * k + 2 * i]; a.hi = acc[8 * k + 2 * i + 1];
-            a = f2_fma(v[i], k < 2 ? sa : sb, a);
-            acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
-          }
-        }
+        q[u][s] = __ldcs(reinterpret_cast<const uint4*>(r + 16 * p));
+        sf[u][s] = __ldcs(reinterpret_cast<const unsigned short*>(r + kValueBytes + 2 * p));
+        rsv[u][s] = src.rs[s] ? __ldg(src.rs[s] + row) : src.gs[s];
       }
-    };
-    if (lane == 0 && pending_store) bulk_wait_source_free<0>();
-    __syncwarp();
-    RowScale sc2;
-    if (REENC) {
-      float am = 0.0f;
-#pragma unroll 1
-      for (int j = 0; j < 6; j++) { float acc[32]; sum_pair(lane + 32 * j, acc); am = absmax32(acc, am); }
-      sc2 = row_scale_from_amax(warp_max(am));
     }
-#pragma unroll 1
-    for (int j = 0; j < 6; j++) {
-      const int p = lane + 32 * j;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int row = row0 + u;
+      if (row >= rows) break;           // uniform over the team
       float acc[32];
-      sum_pair(p, acc);
+      zero32(acc);
+#pragma unroll
+      for (int s = 0; s < NS; s++) decode_acc_natural(acc, q[u][s], sf[u][s], rsv[u][s]);
       if (REENC) {
-        uint4 q;
-        uint32_t sf2 = encode_pair_f32<true>(acc, sc2.inv, q);   // slot order in, slot order out
-        // decode of the re-encoding, still in slot order
-        zero32(acc);
-        {
-          const F2 e = e4m3_unpack2(sf2);
-          const F2 sa = f2_splat(__fmul_rn(e.lo, sc2.rs)), sb = f2_splat(__fmul_rn(e.hi, sc2.rs));
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        float g6[kTeamWarps];
+        team_exchange6(xchg, phase, warp, lane, warp_max(absmax32(acc, 0.0f)), g6);
+        float am = g6[0];
 #pragma unroll
-          for (int k = 0; k < 4; k++) {
-            F2 v[4];
-            e2m1_unpack8(w[k], v);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              F2 a; a.lo = 0.0f; a.hi = 0.0f;
-              a = f2_fma(v[i], k < 2 ? sa : sb, a);
-              acc[8 * k + 2 * i] = a.lo; acc[8 * k + 2 * i + 1] = a.hi;
-            }
-          }
-        }
-        perm4(q.x, q.y, q.z, q.w, f);
-        if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
+        for (int g = 1; g < kTeamWarps; g++) am = fmaxf(am, g6[g]);
+        const RowScale sc2 = row_scale_from_amax(am);
+        uint4 qq;
+        const uint32_t sf2 = encode_pair_f32<true>(acc, [&](float b0, float b1, float& m0, float& m1) {
+          return pair_block_scales(b0, b1, sc2.inv, m0, m1);
+        }, qq);
         char* r = rec_out + (size_t)row * kRecStride;
-        *reinterpret_cast<uint4*>(r + 16 * p) = q;
+        *reinterpret_cast<uint4*>(r + 16 * p) = qq;
         *reinterpret_cast<uint16_t*>(r + kValueBytes + 2 * p) = (uint16_t)sf2;
+        if (p == 0) {
+          const uint32_t b = __float_as_uint(sc2.rs);
+          *reinterpret_cast<uint4*>(r + kQRowBytes) = make_uint4(b, b, b, b);
+        }
+        zero32(acc);
+        decode_acc_natural(acc, qq, sf2, sc2.rs);       // every rank outputs the decode of the re-encoding
       }
       uint4 o[4];
       pack32_bf16(acc, o);
-#pragma unroll
-      for (int k = 0; k < 4; k++) sts16(ws.o + p * 64 + ((k ^ f) << 4), o[k]);
+      stage_out(stage, lane, o, out + (size_t)row * kRowB + warp * kStageBytes);
     }
-    if (REENC && lane == 0) {
-      const uint32_t b = __float_as_uint(sc2.rs);
-      *reinterpret_cast<uint4*>(rec_out + (size_t)row * kRecStride + kQRowBytes) = make_uint4(b, b, b, b);
-    }
-    fence_smem_to_async();
-    __syncwarp();
-    if (lane == 0) { bulk_store(out + (size_t)row * kRowB, ws.o, kRowB); bulk_commit(); }
-    pending_store = true;
   }
-  if (lane == 0) bulk_wait_done<0>();
 }
 
 // ---------------------------------------------------------------------------------------------
 // add + Gemma RMSNorm:  z = x + res, res_out = bf16(z), y = (bf16(z) * rinv) * (wbias + w)
+// The sum of squares follows the fixed tree of the host model: per pair (t0 + t1) + (t2 + t3) over its four
+// chunk sums, a butterfly over the 32 pairs of a group (= one warp here), then the six groups in order.
 // ---------------------------------------------------------------------------------------------
 template <int EPI>
-__global__ void __launch_bounds__(kOpsWarps * 32, 1)
+__global__ void __launch_bounds__(kTeamThreads, 3)
 add_rmsnorm_kernel(const char* __restrict__ x, const char* __restrict__ res_in, char* res_out,
                    const char* __restrict__ weight, float eps, float wbias, float qscale, char* out, char* outq,
-                   int rows, uint32_t* err) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int f = (lane >> 1) & 3;
-  WarpSmem ws = carve(smem, warp);
-  if (lane == 0) { mbar_init(ws.bar, 1); }
-  mbar_init_fence();
-  __syncwarp();
-  const int stride = gridDim.x * kOpsWarps;
-  int it = 0;
-  for (int row = blockIdx.x * kOpsWarps + warp; row < rows; row += stride, it++) {
-    if (lane == 0) {
-      bulk_wait_source_free<0>();     // the previous row's stores have left the buffers
-      mbar_arrive_expect(ws.bar, 2 * kRowB);
-      bulk_load(ws.a, x + (size_t)row * kRowB, kRowB, ws.bar);
-      bulk_load(ws.b, res_in + (size_t)row * kRowB, kRowB, ws.bar);
+                   int rows) {
+  __shared__ __align__(128) uint8_t stage_all[kTeamWarps * kStageBytes];
+  __shared__ float xchg[16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, p = threadIdx.x;
+  uint8_t* stage = stage_all + warp * kStageBytes;
+  int phase = 0;
+  // this thread's 32 weights never change: fetched once
+  uint4 wt[4];
+  {
+    uint4 raw[4];
+    load_issue(weight + warp * kStageBytes, lane, raw);
+    stage_in(stage, lane, raw, wt);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint4 rx[4], rr[4];
+    load_issue(x + (size_t)row * kRowB + warp * kStageBytes, lane, rx);
+    load_issue(res_in + (size_t)row * kRowB + warp * kStageBytes, lane, rr);
+    uint4 cx[4], cr[4];
+    stage_in(stage, lane, rx, cx);
+    stage_in(stage, lane, rr, cr);
+    float acc[32];
+    {
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(cx);
+#pragma unroll
+      for (int i = 0; i < 16; i++) { const F2 t = bf16x2_to_f2(xw[i]); acc[2 * i] = t.lo; acc[2 * i + 1] = t.hi; }
     }
-    wait_row(ws.bar, (uint32_t)(it & 1), err);
-    uint4 zb[6][4];
-    float g6[6];
-#pragma unroll
-    for (int j = 0; j < 6; j++) {
-      const int p = lane + 32 * j;
-      float acc[32];
-      uint4 r[4];
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        const uint4 c = lds16(ws.a + p * 64 + ((k ^ f) << 4));
-        const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) { const F2 t = bf16x2_to_f2(cw[i]); acc[8 * k + 2 * i] = t.lo; acc[8 * k + 2 * i + 1] = t.hi; }
-        r[k] = lds16(ws.b + p * 64 + ((k ^ f) << 4));
-      }
-      const float sp = add_residual_sumsq(acc, r);
-      pack32_bf16(acc, zb[j]);
-#pragma unroll
-      for (int k = 0; k < 4; k++) sts16(ws.b + p * 64 + ((k ^ f) << 4), zb[j][k]);
-      g6[j] = warp_sum_butterfly(sp);
-    }
-    fence_smem_to_async();
-    __syncwarp();
-    if (lane == 0) bulk_store(res_out + (size_t)row * kRowB, ws.b, kRowB);
+    const float sp = add_residual_sumsq(acc, cr);
+    uint4 zb[4];
+    pack32_bf16(acc, zb);
+    stage_out(stage, lane, zb, res_out + (size_t)row * kRowB + warp * kStageBytes);
+    float g6[kTeamWarps];
+    team_exchange6(xchg, phase, warp, lane, warp_sum_butterfly(sp), g6);
     float ss = g6[0];
 #pragma unroll
-    for (int g = 1; g < 6; g++) ss = __fadd_rn(ss, g6[g]);
+    for (int g = 1; g < kTeamWarps; g++) ss = __fadd_rn(ss, g6[g]);
     const float rinv = norm_rinv(ss, eps);
-#pragma unroll
-    for (int j = 0; j < 6; j++) {
-      const int p = lane + 32 * j;
-      uint4 wt[4];
-#pragma unroll
-      for (int k = 0; k < 4; k++) wt[k] = __ldg(reinterpret_cast<const uint4*>(weight + p * 64 + ((k ^ f) << 4)));
-      float y[32];
-      norm_pair(zb[j], wt, rinv, wbias, y);
-      uint4 yb[4];
-      pack32_bf16(y, yb);
-      if (EPI == 1) {
-#pragma unroll
-        for (int k = 0; k < 4; k++) sts16(ws.o + p * 64 + ((k ^ f) << 4), yb[k]);
-      } else if (EPI == 2) {
-        uint4 q;
-        uint32_t sf2 = quant_pair_nvfp4_out(yb, qscale, q);
-        perm4(q.x, q.y, q.z, q.w, f);
-        if (f & 2) sf2 = ((sf2 & 0xffu) << 8) | (sf2 >> 8);
-        sts16(ws.o + p * 16, q);
-        *reinterpret_cast<uint16_t*>(ws.o + kValueBytes + 2 * p) = (uint16_t)sf2;
-      } else {
-        uint4 v[2];
-        const uint32_t e = quant_pair_mxfp8_out(yb, v);
-        const uint32_t* vw = reinterpret_cast<const uint32_t*>(v);
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-          *reinterpret_cast<uint2*>(ws.o + p * 32 + ((k ^ f) << 3)) = make_uint2(vw[2 * k], vw[2 * k + 1]);
-        ws.o[kHidden + p] = (uint8_t)e;
-      }
-    }
-    fence_smem_to_async();
-    __syncwarp();
-    if (lane == 0) {
-      if (EPI == 1) bulk_store(out + (size_t)row * kRowB, ws.o, kRowB);
-      else if (EPI == 2) bulk_store(outq + (size_t)row * kQRowBytes, ws.o, kQRowBytes);
-      else bulk_store(outq + (size_t)row * kMxRowBytes, ws.o, kMxRowBytes);
-      bulk_commit();
+    float y[32];
+    norm_pair(zb, wt, rinv, wbias, y);
+    uint4 yb[4];
+    pack32_bf16(y, yb);
+    if (EPI == 1) {
+      stage_out(stage, lane, yb, out + (size_t)row * kRowB + warp * kStageBytes);
+    } else if (EPI == 2) {
+      uint4 q;
+      const uint32_t sf2 = quant_pair_nvfp4_out(yb, qscale, q);
+      char* r = outq + (size_t)row * kQRowBytes;
+      __stcs(reinterpret_cast<uint4*>(r + 16 * p), q);
+      *reinterpret_cast<uint16_t*>(r + kValueBytes + 2 * p) = (uint16_t)sf2;
+    } else {
+      uint4 v[2];
+      const uint32_t e = quant_pair_mxfp8_out(yb, v);
+      char* r = outq + (size_t)row * kMxRowBytes;
+      __stcs(reinterpret_cast<uint4*>(r + 32 * p), v[0]);
+      __stcs(reinterpret_cast<uint4*>(r + 32 * p + 16), v[1]);
+      r[kHidden + p] = (char)(uint8_t)e;
     }
   }
-  if (lane == 0) bulk_wait_done<0>();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -270,56 +297,11 @@ __global__ void fill_sentinel_kernel(uint4* win, size_t buf_units, int nbuf) {
   }
 }
 
-// A word the kernels above set when a local row load did not arrive in time.
-// One word per device for the whole process (allocated on the first use on that device, never freed).
-static uint32_t* ops_error_word() {
-  static std::mutex mu;
-  static std::atomic<uint32_t*> p[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  uint32_t* w = p[dev].load(std::memory_order_acquire);
-  if (w) return w;
-  std::lock_guard<std::mutex> lock(mu);
-  w = p[dev].load(std::memory_order_acquire);
-  if (!w) {
-    if (cudaMalloc(&w, 16) != cudaSuccess) return nullptr;
-    cudaMemset(w, 0, 16);
-    p[dev].store(w, std::memory_order_release);
-  }
-  return w;
-}
-
-static int ops_grid(int rows) {
-  const int sms = device_sm_count();
-  const int need = (rows + kOpsWarps - 1) / kOpsWarps;
-  return need < sms ? (need > 0 ? need : 1) : sms;
-}
-
-// Raises a kernel's dynamic shared-memory limit once per (kernel, device); later calls are two atomic loads.
-// (Every kernel of this file is launched with the one size kOpsSmem.)
-struct SmemRaised {
-  std::atomic<const void*> fn{nullptr};
-  std::atomic<unsigned long long> devices{0};   // bit d: done on device d
-};
-static SmemRaised g_smem_raised[64];
-template <class K>
-static bool ensure_smem(K kernel, int bytes) {
-  const void* key = reinterpret_cast<const void*>(kernel);
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return false;
-  SmemRaised* slot = nullptr;
-  for (SmemRaised& e : g_smem_raised) {
-    const void* cur = e.fn.load(std::memory_order_acquire);
-    if (cur == nullptr) {
-      const void* expected = nullptr;
-      if (e.fn.compare_exchange_strong(expected, key, std::memory_order_acq_rel)) cur = key; else cur = expected;
-    }
-    if (cur == key) { slot = &e; break; }
-  }
-  if (slot && dev >= 0 && dev < 64 && ((slot->devices.load(std::memory_order_acquire) >> dev) & 1ull)) return true;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
-  if (slot && dev >= 0 && dev < 64) slot->devices.fetch_or(1ull << dev, std::memory_order_release);
-  return true;
+// Persistent grid of row teams: enough CTAs to fill every SM `per_sm` times, never more than there are trips.
+static int team_grid(int rows, int rows_per_trip, int per_sm) {
+  const int trips = (rows + rows_per_trip - 1) / rows_per_trip;
+  const int cap = device_sm_count() * per_sm;
+  return trips < cap ? (trips > 0 ? trips : 1) : cap;
 }
 
 }  // namespace fp4ar
@@ -332,10 +314,8 @@ extern "C" int fp4ar_encode(const void* x, int rows, void* values, long vpitch, 
   if (((uintptr_t)x | (uintptr_t)values | (uintptr_t)vpitch) & 15) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)scales | (uintptr_t)spitch) & 1) return FP4AR_ERR_ARGUMENT;
   if (rows == 0) return FP4AR_OK;
-  uint32_t* err = ops_error_word();
-  if (!err || !ensure_smem(encode_rows_kernel<false>, kOpsSmem)) return cuda_fail();
-  encode_rows_kernel<false><<<ops_grid(rows), kOpsWarps * 32, kOpsSmem, (cudaStream_t)stream>>>(
-      (const char*)x, rows, (char*)values, vpitch, (char*)scales, spitch, row_scales, 0.0f, err);
+  encode_rows_kernel<false><<<team_grid(rows, 2, 4), kTeamThreads, 0, (cudaStream_t)stream>>>(
+      (const char*)x, rows, (char*)values, vpitch, (char*)scales, spitch, row_scales, 0.0f);
   return cuda_check_launch();
 }
 
@@ -343,10 +323,8 @@ extern "C" int fp4ar_encode_static(const void* x, int rows, float gs, void* qrow
   if (!x || !qrows || rows < 0 || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)qrows) & 15) return FP4AR_ERR_ARGUMENT;
   if (rows == 0) return FP4AR_OK;
-  uint32_t* err = ops_error_word();
-  if (!err || !ensure_smem(encode_rows_kernel<true>, kOpsSmem)) return cuda_fail();
-  encode_rows_kernel<true><<<ops_grid(rows), kOpsWarps * 32, kOpsSmem, (cudaStream_t)stream>>>(
-      (const char*)x, rows, (char*)qrows, kQRowBytes, (char*)qrows + kValueBytes, kQRowBytes, nullptr, 1.0f / gs, err);
+  encode_rows_kernel<true><<<team_grid(rows, 2, 4), kTeamThreads, 0, (cudaStream_t)stream>>>(
+      (const char*)x, rows, (char*)qrows, kQRowBytes, (char*)qrows + kValueBytes, kQRowBytes, nullptr, 1.0f / gs);
   return cuda_check_launch();
 }
 
@@ -364,11 +342,11 @@ static int launch_decode(int nsrc, const void* const* src, long pitch, const flo
     if (!sl.rs[s]) { if (!gs) return FP4AR_ERR_ARGUMENT; sl.gs[s] = gs[s]; }
   }
   if (rows == 0) return FP4AR_OK;
-  const int grid = ops_grid(rows), blk = kOpsWarps * 32;
-#define FP4AR_DEC_CASE(N)                                                                                   \
-  case N:                                                                                                   \
-    if (!ensure_smem(decode_sum_kernel<N, REENC>, kOpsSmem)) return cuda_fail();                             \
-    decode_sum_kernel<N, REENC><<<grid, blk, kOpsSmem, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);  \
+  const int per_trip = nsrc == 1 ? 4 : (nsrc == 2 ? 2 : 1);
+  const int grid = team_grid(rows, per_trip, (nsrc > 4 || REENC) ? 3 : 4);
+#define FP4AR_DEC_CASE(N)                                                                                          \
+  case N:                                                                                                          \
+    decode_sum_kernel<N, REENC><<<grid, kTeamThreads, 0, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);       \
     break;
   switch (nsrc) {
     FP4AR_DEC_CASE(1) FP4AR_DEC_CASE(2) FP4AR_DEC_CASE(3) FP4AR_DEC_CASE(4)
@@ -396,16 +374,13 @@ extern "C" int fp4ar_add_rmsnorm(const void* x, const void* res_in, void* res_ou
   if (((uintptr_t)x | (uintptr_t)res_in | (uintptr_t)res_out | (uintptr_t)weight | (uintptr_t)out | (uintptr_t)outq) & 15)
     return FP4AR_ERR_ARGUMENT;
   if (rows == 0) return FP4AR_OK;
-  uint32_t* err = ops_error_word();
-  if (!err) return cuda_fail();
-  const int grid = ops_grid(rows), blk = kOpsWarps * 32;
+  const int grid = team_grid(rows, 1, 3);
   cudaStream_t st = (cudaStream_t)stream;
 #define FP4AR_NORM_CASE(E)                                                                                         \
   case E:                                                                                                          \
-    if (!ensure_smem(add_rmsnorm_kernel<E>, kOpsSmem)) return cuda_fail();                                          \
-    add_rmsnorm_kernel<E><<<grid, blk, kOpsSmem, st>>>((const char*)x, (const char*)res_in, (char*)res_out,        \
-                                                       (const char*)weight, eps, wbias, qscale, (char*)out,        \
-                                                       (char*)outq, rows, err);                                    \
+    add_rmsnorm_kernel<E><<<grid, kTeamThreads, 0, st>>>((const char*)x, (const char*)res_in, (char*)res_out,      \
+                                                         (const char*)weight, eps, wbias, qscale, (char*)out,      \
+                                                         (char*)outq, rows);                                       \
     break;
   switch (epilogue) { FP4AR_NORM_CASE(1) FP4AR_NORM_CASE(2) FP4AR_NORM_CASE(3) }
 #undef FP4AR_NORM_CASE

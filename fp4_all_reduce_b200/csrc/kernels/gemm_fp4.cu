@@ -272,7 +272,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         }
         uint4 qv;
-        const uint32_t sf2 = encode_pair_f32<true>(v, p.inv_gs, qv);
+        const uint32_t sf2 = encode_pair_f32<true>(v, [&](float b0, float b1, float& m0, float& m1) {
+          return pair_block_scales(b0, b1, p.inv_gs, m0, m1);
+        }, qv);
         *reinterpret_cast<uint4*>(my_piece + 16 * c) = qv;
         *reinterpret_cast<uint16_t*>(my_piece + S::kValueB + 2 * c) = (uint16_t)sf2;
       }

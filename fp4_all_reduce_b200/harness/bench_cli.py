@@ -87,6 +87,9 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--nccl-only", action="store_true", help="skip the fused-kernel cells (NCCL sweeps)")
+    ap.add_argument("--nccl-reg", action="store_true",
+                    help="also time NCCL on buffers allocated with ncclMemAlloc and registered with the communicator")
     ap.add_argument("--tag", default="")
     ap.add_argument("--out", default=None)
     ns = ap.parse_args(argv)
@@ -110,10 +113,12 @@ def main(argv=None) -> int:
         if rank == 0:
             print(json.dumps(rec), flush=True)
 
-    def timed(fn):
+    def timed(fn, before_each=None):
         g = timing.capture(fn, ns.graph, dev, warm_calls=2)
+        if before_each is not None:
+            before_each()
         with ClockSampler(local) as clk:
-            t = timing.time_replays(g, ns.graph, ns.iters, ns.warmup, dev)
+            t = timing.time_replays(g, ns.graph, ns.iters, ns.warmup, dev, before_each=before_each)
         c = clk.summary()
         del g
         return t, c
@@ -123,7 +128,7 @@ def main(argv=None) -> int:
             for epi in (int(e) for e in ns.epilogues.split(",")):
                 cell = Cell(rows, INPUTS[inp], epi, rank, world, dev)
                 cell.variant = ns.variant
-                for algo in ns.algos.split(","):
+                for algo in ([] if ns.nccl_only else ns.algos.split(",")):
                     for tw in (int(t) for t in ns.team_warps.split(",")):
                         for teams, lags in ((int(t), int(l)) for t in ns.teams.split(",") for l in ns.lags.split(",")):
                             res = {}
@@ -148,22 +153,55 @@ def main(argv=None) -> int:
                                 emit({**common, "kind": "overlap", "rows": rows, "input": inp, "epilogue": epi, "algo": algo,
                                       "team_warps": tw, "teams": teams,
                                       "corrected_overlap": round((X + Cc - F - E) / den, 3) if den > 0 else None})
-                if ns.nccl and inp == "bf16" and world > 1:
-                    buf = [D.partial(rows, rank).to(dev) for _ in range(cell.nsets)]
+                if ns.nccl and inp == "bf16" and world > 1 and epi <= 1:
+                    # NCCL reduces in place: one buffer per call of the graph, every buffer restored from the pristine
+                    # partial before each replay (outside the events), so every all-reduce sums fresh, finite data.
+                    pristine = D.partial(rows, rank).to(dev)
+                    arms = [("", None)]
+                    if ns.nccl_reg:
+                        arms.append(("_reg", "registered"))
+                    for suffix, reg in arms:
+                        pool = None
+                        try:
+                            if reg:
+                                # user-buffer registration: memory from ncclMemAlloc, registered with the communicator
+                                # (the reference's registered arm: harness/fp4ar_bench.cu:453-457)
+                                backend = dist.distributed_c10d._get_default_group()._get_backend(dev)
+                                pool = torch.cuda.MemPool(backend.mem_allocator)
+                                with torch.cuda.use_mem_pool(pool):
+                                    buf = [torch.empty_like(pristine) for _ in range(ns.graph)]
+                                backend.register_mem_pool(pool)
+                            else:
+                                buf = [torch.empty_like(pristine) for _ in range(ns.graph)]
+                        except Exception as e:
+                            emit({**common, "variant": "nccl_bf16" + suffix, "rows": rows, "epilogue": epi,
+                                  "skipped": f"{type(e).__name__}: {str(e)[:160]}"})
+                            continue
 
-                    def nccl_fn(i):
-                        dist.all_reduce(buf[i % len(buf)])
-                        if epi:
-                            codec.add_rmsnorm(buf[i % len(buf)], cell.res, cell.w, inplace_residual=True, out=cell.out,
-                                              epilogue=N.EPI_NORM_BF16)
-                    if epi <= 1:
-                        t, c = timed(nccl_fn)
-                        emit({**common, "variant": "nccl_bf16" + ("+norm" if epi else ""), "mode": "fused", "rows": rows,
+                        def restore(buf=buf):
+                            for b in buf:
+                                b.copy_(pristine)
+
+                        def nccl_fn(i, buf=buf):
+                            dist.all_reduce(buf[i % len(buf)])
+                            if epi:
+                                codec.add_rmsnorm(buf[i % len(buf)], cell.res, cell.w, inplace_residual=True, out=cell.out,
+                                                  epilogue=N.EPI_NORM_BF16)
+                        t, c = timed(nccl_fn, before_each=restore)
+                        emit({**common, "variant": "nccl_bf16" + suffix + ("+norm" if epi else ""), "mode": "fused", "rows": rows,
                               "input": "bf16", "epilogue": epi, "med_us": round(t["med_us"], 3),
                               "p10_us": round(t["p10_us"], 3), "p90_us": round(t["p90_us"], 3),
-                              "sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons"),
-                              "proto": os.environ.get("NCCL_PROTO", "default"), "nccl_algo": os.environ.get("NCCL_ALGO", "default")})
-                    del buf
+                              "sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons"), "registered": bool(reg),
+                              "proto": os.environ.get("NCCL_PROTO", "default"), "nccl_algo": os.environ.get("NCCL_ALGO", "default"),
+                              "nchannels": os.environ.get("NCCL_MIN_NCHANNELS", "default")})
+                        del buf
+                        if pool is not None:
+                            try:
+                                backend.deregister_mem_pool(pool)
+                            except Exception:
+                                pass
+                            del pool
+                    del pristine
                 del cell
                 torch.cuda.empty_cache()
     if rank == 0 and ns.out:

@@ -66,6 +66,7 @@ class InputSet:
     weight: Optional[torch.Tensor]
     exp: dict = field(default_factory=dict)      # host model outputs (numpy)
     exact: Optional[np.ndarray] = None           # exact FP32 sum of the BF16 partials
+    exp_dev: dict = field(default_factory=dict)  # the same outputs on the device (bit patterns), for the compares
 
 
 def _gen(cfg: CellConfig, rank: int, set_id: int) -> torch.Tensor:
@@ -108,7 +109,15 @@ def make_inputs(cfg: CellConfig, set_id: int, device) -> InputSet:
         res_bits, w_bits = O.bf16_bits(res), O.bf16_bits(weight)
     exp = O.allreduce(model_in, algo=cfg.resolved_algo(), input_kind=kind, gs=gs, epi=cfg.epilogue, res_in=res_bits,
                       weight=w_bits, eps=cfg.eps, wbias=cfg.weight_bias, qscale=cfg.qscale)
-    return InputSet(xs_dev, gs, res, weight, exp, exact)
+    # The expectation is uploaded once: the per-call compares then run on the device (a 16K-row output is 200 MB;
+    # bringing it to the host after every call would dominate the gate's run time on a multi-GPU machine).
+    exp_dev = {}
+    for k in ("out", "outq", "res_out"):
+        v = exp.get(k)
+        if v is not None:
+            a = np.ascontiguousarray(v)
+            exp_dev[k] = torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).to(device)
+    return InputSet(xs_dev, gs, res, weight, exp, exact, exp_dev)
 
 
 class Outputs:
@@ -148,10 +157,24 @@ def _mism(t: Optional[torch.Tensor], want: Optional[np.ndarray]) -> int:
     return int(np.count_nonzero(t.cpu().numpy() != want))
 
 
+def _mism_dev(t: Optional[torch.Tensor], want: Optional[torch.Tensor]) -> int:
+    """The same count on the device: `want` holds the model's bit patterns (int16 for BF16 outputs, uint8 otherwise)."""
+    if t is None:
+        return 0
+    if t.dtype == torch.bfloat16:
+        got = t.view(torch.int16)
+        gn = (got & 0x7FFF) > 0x7F80
+        wn = (want & 0x7FFF) > 0x7F80
+        return int(((got != want) & ~(gn & wn)).sum().item())
+    return int((t != want).sum().item())
+
+
 def mismatches(cfg: CellConfig, inp: InputSet, outs: Outputs, local: int) -> int:
     """Number of differing output elements of one local rank against the host model."""
-    return (_mism(outs.out[local], inp.exp["out"]) + _mism(outs.outq[local], inp.exp["outq"]) +
-            _mism(outs.res_out[local], inp.exp["res_out"]))
+    pairs = ((outs.out[local], "out"), (outs.outq[local], "outq"), (outs.res_out[local], "res_out"))
+    if all(t is None or k in inp.exp_dev for t, k in pairs):
+        return sum(_mism_dev(t, inp.exp_dev.get(k)) for t, k in pairs)
+    return sum(_mism(t, inp.exp[k]) for t, k in pairs)
 
 
 def rel_l2(inp: InputSet, out_bits: np.ndarray) -> float:

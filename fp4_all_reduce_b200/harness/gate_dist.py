@@ -34,7 +34,7 @@ ALGO_NAMES = {"auto": N.ALGO_AUTO, "oneshot": N.ALGO_ONESHOT, "twoshot": N.ALGO_
 
 
 def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int, graph_reps: int, skew_reps: int,
-              skew_us: float, negctl: str | None) -> dict:
+              skew_us: float, negctl: str | None, percall: int = 0) -> dict:
     dev = ctx.device
     rank, world = ctx.rank, ctx.nranks
     sets = [make_inputs(cfg, s, dev) for s in range(3)]
@@ -87,7 +87,7 @@ def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int
     rec["mism_b2b_final"] = total(compare(reps))
     # 3: compare after every call
     bad = mm = 0
-    per = max(3, reps // 5)
+    per = percall if percall > 0 else max(3, reps // 5)
     for s in range(per):
         outs.clear()
         call(s)
@@ -155,6 +155,9 @@ def main(argv=None) -> int:
     ap.add_argument("--skew-us", type=float, default=50.0)
     ap.add_argument("--negctl", default=None, choices=[None, "stale", "flip", "bias"])
     ap.add_argument("--timeout-ms", type=int, default=1000)
+    ap.add_argument("--team-warps", default="0", help="comma list of warps per row team (0 = the library's default)")
+    ap.add_argument("--lags", default="0", help="comma list of two-shot depths, lag_owner + 16 * lag_finish (0 = default)")
+    ap.add_argument("--percall", type=int, default=0, help="calls with a compare after each (0 = reps / 5, at least 3)")
     ap.add_argument("--out", default=None)
     ns = ap.parse_args(argv)
 
@@ -172,12 +175,14 @@ def main(argv=None) -> int:
     for rows in rows_list:
         for inp in ns.inputs.split(","):
             for epi in (int(e) for e in ns.epilogues.split(",")):
-                for algo in ns.algos.split(","):
+                for algo, tw, lags in ((a, int(t), int(l)) for a in ns.algos.split(",") for t in ns.team_warps.split(",")
+                                       for l in ns.lags.split(",")):
                     cfg = CellConfig(nranks=world, rows=rows, algo=ALGO_NAMES[algo], input=IN_NAMES[inp], epilogue=epi,
-                                     dist=ns.dist)
+                                     dist=ns.dist, team_warps=tw, lags=lags)
                     t0 = time.time()
                     rec = gate_cell(ctx, cfg, reps=ns.reps, graph_calls=ns.graph_calls, graph_reps=ns.graph_reps,
-                                    skew_reps=ns.skew_reps, skew_us=ns.skew_us, negctl=ns.negctl)
+                                    skew_reps=ns.skew_reps, skew_us=ns.skew_us, negctl=ns.negctl, percall=ns.percall)
+                    rec["team_warps"], rec["lags"] = tw, lags
                     rec["seconds"] = round(time.time() - t0, 2)
                     rec["sources"] = sources_digest()
                     fails += not rec["pass"]

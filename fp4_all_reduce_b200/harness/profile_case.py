@@ -16,25 +16,9 @@ import sys
 import torch
 
 from .. import _native as N
-from ..parallel.context import EmulatedGroup, Fp4ArContext, make_args
+from ..parallel.context import EmulatedGroup, Fp4ArContext, SoloRankContext, make_args
 from ..utils import data as D
 from ..ops import codec
-
-
-class _SoloRank(Fp4ArContext):
-    """Rank 0 of an nranks group with every window on this GPU; only usable in compute (loop-back) mode."""
-
-    def __init__(self, nranks, rows, dev):
-        import ctypes as C
-        self.group, self.rank, self.nranks, self.max_rows, self.device = None, 0, nranks, rows, dev
-        lib = N.cuda()
-        self.window_bytes = int(lib.fp4ar_window_bytes(rows, N.HIDDEN, nranks))
-        self.window = torch.empty(self.window_bytes, dtype=torch.uint8, device=dev)
-        self._handle = None
-        ptrs = (C.c_void_p * nranks)(*([self.window.data_ptr()] * nranks))
-        ctx = C.c_void_p()
-        N.check(lib.fp4ar_create(C.byref(ctx), 0, nranks, dev.index or 0, rows, N.HIDDEN, ptrs, self.window_bytes), "fp4ar_create")
-        self._ctx = ctx
 
 
 def main(argv=None) -> int:
@@ -78,7 +62,7 @@ def main(argv=None) -> int:
     if ns.solo:
         if ns.mode != N.MODE_COMPUTE:
             raise SystemExit("--solo needs --mode 2 (a rank launched alone would wait for peers that never run)")
-        ctx = _SoloRank(P, rows, dev)
+        ctx = SoloRankContext(P, rows, dev)
         a0 = args(0)
         launch = lambda: ctx.launch(a0)
     elif P == 1:

@@ -19,7 +19,11 @@ What is checked on every schedule:
   * the system never deadlocks, and at the end every slot of every window is SENTINEL again.
 
 `variant` switches one protocol rule off to show that the checker can fail: "one_buffer" (no call parity) and
-"no_drain" (a call may end before its own stores have landed) must both produce violations.
+"no_drain" (a call may end before its own stores have landed) must both produce violations.  So must
+"empty_call_bumps": a call that exchanges nothing (zero rows) but still advances the call counter lets a fast rank
+reach the buffer parity that a slow rank is still consuming; the runtime therefore launches nothing for a zero-row
+call ("empty_call_skipped", safe), and loop-back (compute-mode) calls, which do advance the counter, need a barrier
+before the next fused call.
 
 The reference project argues the same properties on paper (docs/DESIGN.md:122-128) and probes them with rotating
 input sets and skewed ranks on GPUs; this is the exhaustive-in-spirit counterpart that needs no GPU and is where a
@@ -63,6 +67,8 @@ class Model:
     dead_rank: int = -1             # this rank stops before pushing anything in call `dead_call`
     dead_call: int = 0
     wait_limit: int = 2000          # scheduler steps a blocked wait may last when a rank is dead
+    empty_calls: tuple = ()         # program positions at which every rank issues a call that exchanges nothing
+    empty_bumps: bool = False       # whether such a call advances the device call counter (the buffer parity)
     rng: random.Random = field(init=False)
     win: list = field(init=False)
     inflight: list = field(init=False)
@@ -93,9 +99,18 @@ class Model:
     # ------------------------------------------------------------------ one rank
     def rank_program(self, me: int):
         P, R = self.P, self.rows
-        for c in range(self.calls):
-            if me == self.dead_rank and c >= self.dead_call:
+        counter = 0                      # the device call counter of this rank
+        for pos in range(self.calls):
+            if me == self.dead_rank and pos >= self.dead_call:
                 return
+            if pos in self.empty_calls:
+                # a call with nothing to exchange (zero rows; or a loop-back call, which only touches the own window)
+                if self.empty_bumps:
+                    counter += 1
+                yield None
+                continue
+            c = counter
+            counter += 1
             buf = c % self.nbuf
 
             def push(dst, slot, rec):
@@ -201,10 +216,11 @@ def check(P: int, rows: int, calls: int, *, two_shot: bool, lag_o: int = 1, lag_
     """Run `seeds` random schedules; returns {'schedules', 'violations', 'first'}."""
     nbuf = 1 if variant == "one_buffer" else 2
     drain = variant != "no_drain"
+    empty = tuple(range(1, calls, 2)) if variant.startswith("empty_call") else ()
     bad, first = 0, None
     for s in range(seeds):
         m = Model(P, rows, calls, two_shot=two_shot, lag_o=lag_o, lag_f=lag_f, nbuf=nbuf, drain=drain, seed=s,
-                  starve=starve and s % 2 == 1)
+                  starve=starve and s % 2 == 1, empty_calls=empty, empty_bumps=variant == "empty_call_bumps")
         try:
             m.run()
         except Violation as e:

@@ -135,6 +135,12 @@ class EmulatedGroup(_Base):
         N.check(N.cuda().fp4ar_reset(self._ctx), "fp4ar_reset")
 
 
+def input_sets_for(rows: int, row_bytes: int, l2_bytes: int = 126 * 1024 * 1024, most: int = 24) -> int:
+    """How many rotating copies of a [rows, row_bytes] input a timed chain needs so that consecutive calls never find
+    their input in the L2 cache (together they exceed twice its size)."""
+    return min(most, max(2, -(-2 * l2_bytes // (rows * row_bytes))))
+
+
 class Fp4ArContext(_Base):
     """One rank of a tensor-parallel group; `group` is a torch.distributed process group (NCCL)."""
 
@@ -261,3 +267,34 @@ class Fp4ArContext(_Base):
                               res_out=res_out, weight=weight, eps=eps, weight_bias=weight_bias, outq=q, qscale=qscale,
                               mode=mode, teams=teams))
         return (o if o is not None else q), res_out
+
+
+class SoloRankContext(Fp4ArContext):
+    """Rank 0 of an `nranks` group created ALONE on one GPU: every "peer" window is this GPU's own window.
+
+    Only the compute mode (`mode=MODE_COMPUTE`: the full codec, owner and epilogue work of one rank, every push
+    looped back into the own window, no wait on a peer) may be launched on it; a fused or transport-only launch
+    would wait for peers that never run and end with a PeerTimeout status.  It is the one-GPU stand-in for a rank
+    of a real group: what a profiler captures, and what `bench.py --gpus 1` times.  The reference project has the
+    same mode (include/fp4ar_api.h:12-16, FP4AR_COMPUTE)."""
+
+    def __init__(self, nranks: int, max_rows: int, device: Optional[torch.device] = None):
+        if device is None or device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.group, self.rank, self.nranks, self.max_rows, self.device = None, 0, nranks, max_rows, device
+        lib = N.cuda()
+        self.window_bytes = int(lib.fp4ar_window_bytes(max_rows, N.HIDDEN, nranks))
+        if self.window_bytes == 0:
+            raise ValueError(f"unsupported group size {nranks} or max_rows {max_rows}")
+        self.window = torch.empty(self.window_bytes, dtype=torch.uint8, device=device)
+        self._handle = None
+        ptrs = (C.c_void_p * nranks)(*([self.window.data_ptr()] * nranks))
+        ctx = C.c_void_p()
+        N.check(lib.fp4ar_create(C.byref(ctx), 0, nranks, device.index or 0, max_rows, N.HIDDEN, ptrs,
+                                 self.window_bytes), "fp4ar_create")
+        self._ctx = ctx
+
+    def launch(self, args: N.Args, stream: Optional[torch.cuda.Stream] = None) -> None:
+        if args.mode != N.MODE_COMPUTE:
+            raise ValueError("a rank created alone can only run compute-mode calls (mode=MODE_COMPUTE)")
+        super().launch(args, stream)

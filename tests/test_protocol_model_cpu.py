@@ -29,3 +29,13 @@ def test_a_rank_that_stops_pushing_ends_in_bounded_waits(two_shot):
     assert out["gave_up"] > 0                     # the survivors' waits ran into their limit and were reported
     assert all(rank != 2 for rank, _call, _slot in m.gave_up)
     assert all(call >= 1 for _rank, call, _slot in m.gave_up)     # the call before the failure completed normally
+
+
+@pytest.mark.parametrize("two_shot,lo,lf", [(False, 0, 1), (True, 1, 2)])
+def test_a_call_without_exchange_must_not_advance_the_call_counter(two_shot, lo, lf):
+    """Zero-row calls between real calls: safe when they launch nothing (what the runtime does), caught when they
+    would flip the buffer parity without any rank having waited for its peers."""
+    bad = check(2, 1, 7, two_shot=two_shot, lag_o=lo, lag_f=lf, seeds=150, variant="empty_call_bumps")
+    assert bad["violations"] > 0, bad
+    good = check(2, 1, 7, two_shot=two_shot, lag_o=lo, lag_f=lf, seeds=150, variant="empty_call_skipped")
+    assert good["violations"] == 0, good["first"]

@@ -22,7 +22,8 @@ def ref():
         import build_ref
     finally:
         sys.path.pop(0)
-    if not Path("/root/reference").exists() and not (ROOT / "baseline" / "_ref" / "libref_oracle.so").exists():
+    ref_dir = build_ref.reference_dir()
+    if not (ref_dir and Path(ref_dir).exists()) and not (ROOT / "baseline" / "_ref" / "libref_oracle.so").exists():
         pytest.skip("reference tree not present")
     lib_path = build_ref.build_host_oracle()
     if lib_path is None:
