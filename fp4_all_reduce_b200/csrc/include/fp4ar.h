@@ -62,11 +62,9 @@ typedef struct fp4ar_args {
   float weight_bias;      /* 1.0 for Gemma RMSNorm */
   void* outq;             /* EPI_NORM_NVFP4: [rows][3456]; EPI_NORM_MXFP8: [rows][6336] */
   float qscale;           /* EPI_NORM_NVFP4: global scale multiplied into the block scales */
-  int tune[4];            /* [0] teams per CTA (0 = default), [1] bit 0: no programmatic dependent launch, bits 8-15: experimental kernel build
-                             (0 = product kernels; 1 = slow poll paths out of line; 2 = six-warp teams x 4 per CTA, with [2] = 6;
-                             both for the two-shot shapes of 4 and 8 ranks only),
-                             [2] warps per row team (0 = default 3; compiled widths: 2, 3, and 6 for the default algorithm of each degree with
-                             no or BF16-norm epilogue),
+  int tune[4];            /* [0] teams per CTA (0 = default), [1] bit 0: no programmatic dependent launch,
+                             [2] warps per row team (0 = default: 6 for two-shot at 4 and 8 ranks, else 3; compiled widths:
+                             3 for every shape, 6 for the two-shot shapes of 4 and 8 ranks),
                              [3] two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default) */
 } fp4ar_args;
 
@@ -114,8 +112,10 @@ int fp4ar_get_push_view(fp4ar_ctx* ctx, int local_rank, fp4ar_push_view* out);
 int fp4ar_ctas_per_rank(fp4ar_ctx* ctx);
 const char* fp4ar_last_cuda_error(void);
 const char* fp4ar_build_info(void);
-/* Teams per CTA of the compiled kernel for this shape (0 = not compiled).  variant 0 = product kernels. */
-int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps, int variant);
+/* Teams per CTA of the compiled kernel for this shape (0 = not compiled). */
+int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps);
+/* Warps per row team a launch uses when tune[2] is 0 (algo: FP4AR_ALGO_ONESHOT / TWOSHOT, already resolved). */
+int fp4ar_default_team_warps(int nranks, int algo);
 
 /* ---- stand-alone codec / norm kernels (single GPU, no window) ---- */
 int fp4ar_encode(const void* x_bf16, int rows, void* values, long values_pitch, void* scales, long scales_pitch,

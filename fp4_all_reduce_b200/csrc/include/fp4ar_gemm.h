@@ -23,10 +23,6 @@ extern "C" {
 
 int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, const void* wt, int M, int N, int K,
                      float gs, void* local_q, float* dbg_acc, fp4ar_stream stream);
-/* Output-tile width of the following fp4ar_gemm_nvfp4 calls of this process: 0 = automatic (128 x 256 tiles),
- * 128 or 256 = forced.  128 x 128 tiles double the tile count for small M (better balance over the persistent
- * CTAs) at a lower per-tile efficiency. */
-int fp4ar_gemm_set_tile_n(int bn);
 /* Status block of the GEMM kernels on the current device (code != 0: a bounded wait gave up). */
 int fp4ar_gemm_status(fp4ar_status_words* out);
 

@@ -2,13 +2,9 @@
 #include "ar_table.h"
 namespace fp4ar {
 void ar_register_p4(ArKernelEntry* out, int* n) {
-  out[(*n)++] = make_entry<4, 1, 0, 0, 2>();
   out[(*n)++] = make_entry<4, 1, 0, 0, 3>();
-  out[(*n)++] = make_entry<4, 1, 0, 1, 2>();
   out[(*n)++] = make_entry<4, 1, 0, 1, 3>();
-  out[(*n)++] = make_entry<4, 1, 0, 2, 2>();
   out[(*n)++] = make_entry<4, 1, 0, 2, 3>();
-  out[(*n)++] = make_entry<4, 1, 0, 3, 2>();
   out[(*n)++] = make_entry<4, 1, 0, 3, 3>();
 }
 }  // namespace fp4ar

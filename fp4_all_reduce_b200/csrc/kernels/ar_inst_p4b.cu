@@ -2,21 +2,13 @@
 #include "ar_table.h"
 namespace fp4ar {
 void ar_register_p4b(ArKernelEntry* out, int* n) {
-  out[(*n)++] = make_entry<4, 1, 1, 0, 2>();
   out[(*n)++] = make_entry<4, 1, 1, 0, 3>();
-  out[(*n)++] = make_entry<4, 1, 1, 1, 2>();
   out[(*n)++] = make_entry<4, 1, 1, 1, 3>();
-  out[(*n)++] = make_entry<4, 1, 1, 2, 2>();
   out[(*n)++] = make_entry<4, 1, 1, 2, 3>();
-  out[(*n)++] = make_entry<4, 1, 1, 3, 2>();
   out[(*n)++] = make_entry<4, 1, 1, 3, 3>();
-  out[(*n)++] = make_entry<4, 1, 2, 0, 2>();
   out[(*n)++] = make_entry<4, 1, 2, 0, 3>();
-  out[(*n)++] = make_entry<4, 1, 2, 1, 2>();
   out[(*n)++] = make_entry<4, 1, 2, 1, 3>();
-  out[(*n)++] = make_entry<4, 1, 2, 2, 2>();
   out[(*n)++] = make_entry<4, 1, 2, 2, 3>();
-  out[(*n)++] = make_entry<4, 1, 2, 3, 2>();
   out[(*n)++] = make_entry<4, 1, 2, 3, 3>();
 }
 }  // namespace fp4ar

@@ -62,12 +62,6 @@ struct ArParams {
   unsigned long long* phase_cycles;   // tuning builds only (-DFP4AR_PHASE_TIMERS): 16 per-phase cycle counters
 };
 
-// Teams per CTA of the six-warp shapes: 3 (18 warps, 112 registers available) unless an experimental translation
-// unit asks for 4 (24 warps, 85 registers); such a unit must also rename the kernel (FP4AR_KERNEL_NAME).
-#ifndef FP4AR_T6_TEAMS
-#define FP4AR_T6_TEAMS 3
-#endif
-
 template <int P, int ALGO, int IN, int EPI, int T>
 struct ArShape {
   static constexpr int NJ = 6 / T;                                   // pairs per lane per row
@@ -89,7 +83,9 @@ struct ArShape {
   // residual: those shapes get fewer, fatter threads.
   // (Register budget per thread = 65536 / (32 * T * kMaxTeams).)
   static constexpr int kHeavy = (ALGO == 1 || EPI > 0) ? 1 : 0;
-  static constexpr int kMaxTeams = T == 2 ? (kHeavy ? 6 : 8) : (T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : FP4AR_T6_TEAMS));
+  // Three-warp teams: 4 per CTA (heavy shapes) or 5; six-warp teams: 3 per CTA (18 warps at up to 112 registers; a
+  // fourth team at 80 registers measured 20-30 % slower).
+  static constexpr int kMaxTeams = T == 3 ? (kHeavy ? 4 : 5) : (T == 1 ? 8 : 3);
   static __host__ __device__ constexpr int smem_bytes(int teams) { return teams * kTeamBytes + kCtaExtra; }
 };
 
@@ -147,51 +143,8 @@ struct TeamSync {
   }
 };
 
-// Experimental build switches, set by the translation unit before this header is included; without them the
-// kernel below is the product kernel, token for token.
-//   FP4AR_KERNEL_NAME   name of the kernel template (default ar_kernel), so a variant can live beside the product
-//   FP4AR_COLD_PATHS    the slow halves of the window polls (loops with the timer and the failure report) become
-//                       calls to out-of-line functions instead of being inlined at each of their ~20 call sites:
-//                       smaller kernel bodies for the instruction cache, identical fast paths and identical results
-#ifndef FP4AR_KERNEL_NAME
-#define FP4AR_KERNEL_NAME ar_kernel
-#endif
-
-#ifdef FP4AR_COLD_PATHS
-static __device__ __noinline__ void cold_poll_pair(const char* rec, int p, uint4& q, uint32_t& sf2, volatile uint32_t* abort_flag,
-                                                   unsigned long long timeout_ns, const WaitCtx& wctx, int row, int src, int phase) {
-  const unsigned long long t0 = global_timer_ns();
-  uint32_t n = 0;
-  while (true) {
-    if (*abort_flag) break;
-    if (values_pending(q)) q = poll_ld16(rec + 16 * p);
-    if (scales_pending(sf2)) sf2 = poll_ld2(rec + kValueBytes + 2 * p);
-    if (!(values_pending(q) | scales_pending(sf2))) break;
-    if ((++n & 127u) == 0u && global_timer_ns() - t0 > timeout_ns) {
-      report_wait_failure(wctx, kStatusPeerTimeout, (uint32_t)row, (uint32_t)src, (uint32_t)phase);
-      break;
-    }
-  }
-}
-static __device__ __noinline__ uint32_t cold_poll_rowscale(const char* rec, volatile uint32_t* abort_flag, unsigned long long timeout_ns,
-                                                         const WaitCtx& wctx, int row, int src, int phase) {
-  uint32_t b = poll_ld4(rec + kQRowBytes);
-  const unsigned long long t0 = global_timer_ns();
-  uint32_t n = 0;
-  while (rowscale_pending(b)) {
-    if (*abort_flag) break;
-    b = poll_ld4(rec + kQRowBytes);
-    if ((++n & 127u) == 0u && global_timer_ns() - t0 > timeout_ns) {
-      report_wait_failure(wctx, kStatusPeerTimeout, (uint32_t)row, (uint32_t)src, (uint32_t)phase);
-      break;
-    }
-  }
-  return b;
-}
-#endif
-
 template <int P, int ALGO, int IN, int EPI, int T>
-__global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTeams, 1) FP4AR_KERNEL_NAME(const __grid_constant__ ArParams prm) {
+__global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTeams, 1) ar_kernel(const __grid_constant__ ArParams prm) {
   using S = ArShape<P, ALGO, IN, EPI, T>;
   constexpr int NJ = S::NJ, NXB = S::NXB, NREC = S::NREC, NSG = S::NSG;
   constexpr bool kTwoShot = S::kTwoShot;
@@ -389,21 +342,6 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   };
 
   // Poll one window record for pair p until its 16 value bytes and 2 scale bytes are sentinel-free.
-#ifdef FP4AR_COLD_PATHS
-  auto poll_pair = [&](const char* rec, int p, uint4& q, uint32_t& sf2, int row, int src, int phase) {
-    q = poll_ld16(rec + 16 * p);
-    sf2 = poll_ld2(rec + kValueBytes + 2 * p);
-    if (values_pending(q) | scales_pending(sf2)) {
-      uint4 tq = q;            // only these copies have their address taken, and only on the slow path
-      uint32_t ts = sf2;
-      cold_poll_pair(rec, p, tq, ts, abort_flag, prm.timeout_ns, wctx, row, src, phase);
-      q = tq; sf2 = ts;
-    }
-  };
-  auto poll_rowscale = [&](const char* rec, int row, int src, int phase) -> float {
-    return __uint_as_float(cold_poll_rowscale(rec, abort_flag, prm.timeout_ns, wctx, row, src, phase));
-  };
-#else
   auto poll_pair = [&](const char* rec, int p, uint4& q, uint32_t& sf2, int row, int src, int phase) {
     q = poll_ld16(rec + 16 * p);
     sf2 = poll_ld2(rec + kValueBytes + 2 * p);
@@ -439,7 +377,6 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
     }
     return __uint_as_float(b);
   };
-#endif
   // i-th rank among the sources that live in the window
   auto window_source = [&](int i) { return IN == 2 ? i : i + (i >= me ? 1 : 0); };
 

@@ -8,7 +8,7 @@
 //                 where the AllReduce kernel in "pushed input" mode finds them, and/or
 //               - into a local [M, N/2 + N/16] NVFP4 tensor.
 //
-// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles (128 x 128 selectable), K in blocks of 64.
+// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.
 //   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
 //                              128-byte swizzle, completion on mbarriers
 //   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
@@ -40,12 +40,12 @@ constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
 
-// Tile width BN: 256 (4-stage ring) is the large-M shape; 128 (6-stage ring) doubles the number of tiles for small M,
-// where 128 x 256 tiles leave the last wave of the 148 persistent CTAs mostly empty.
+// Tile width BN = 256 with a 4-stage ring.  (A 128-wide tile with a 6-stage ring, which doubles the number of tiles
+// for small M, was measured 15-35 % slower at every M from 1024 to 4096 and is not built.)
 template <int BN>
 struct GemmShape {
-  static_assert(BN == 128 || BN == 256, "tile width");
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static_assert(BN == 256, "tile width");
+  static constexpr int kStages = 4;
   static constexpr int kBBytes = BN * kBK * 2;                  // 32 KB / 16 KB
   static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 32 KB
   static constexpr int kValueB = BN / 2, kScaleB = BN / 16;     // 128 + 16 B / 64 + 8 B of one row of one tile
@@ -99,7 +99,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+// Starts the load of 32 accumulator columns of this thread's TMEM lane; the registers are valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -109,8 +110,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// All tcgen05.ld of this thread issued so far have delivered their registers.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 BF16) with the 128-byte
 // swizzle: 8-row groups 1024 bytes apart, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
@@ -262,17 +264,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!__all_sync(0xffffffffu, gemm_wait(acc_full + a, (tile_i >> 1) & 1u, gw, 4))) break;
       tc_fence_after();
       bulk_wait_source_free<0>();   // this thread's previous pieces have left its staging row
-#pragma unroll 1
+      // 32 columns at a time, double-buffered: the load of chunk c + 1 is in flight while chunk c is quantised
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
+      float v[2][32];
+      tmem_ld32_issue(tbase, v[0]);
+#pragma unroll
       for (int c = 0; c < BN / 32; c++) {
-        float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + a * BN + c * 32, v);
+        tmem_ld_wait();
+        if (c + 1 < BN / 32) tmem_ld32_issue(tbase + (c + 1) * 32, v[(c + 1) & 1]);
+        float* vc = v[c & 1];
         if (p.dbg_acc && row < p.M) {
           float4* dst = reinterpret_cast<float4*>(p.dbg_acc + (size_t)row * p.N + n0 + c * 32);
 #pragma unroll
-          for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int i = 0; i < 8; i++) dst[i] = make_float4(vc[4 * i], vc[4 * i + 1], vc[4 * i + 2], vc[4 * i + 3]);
         }
         uint4 qv;
-        const uint32_t sf2 = encode_pair_f32<true>(v, [&](float b0, float b1, float& m0, float& m1) {
+        const uint32_t sf2 = encode_pair_f32<true>(vc, [&](float b0, float b1, float& m0, float& m1) {
           return pair_block_scales(b0, b1, p.inv_gs, m0, m1);
         }, qv);
         *reinterpret_cast<uint4*>(my_piece + 16 * c) = qv;
@@ -283,15 +290,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       fence_smem_to_async();
       if (row < p.M) {
         const size_t voff = (size_t)(n0 / 2), soff = (size_t)(p.N / 2 + n0 / 16);
-        // one row piece to one destination row: values by a bulk store; scales by a bulk store when they fill a
-        // 16-byte granule (BN = 256), else by one 8-byte store from registers (a bulk copy moves multiples of 16 B)
+        // one row piece to one destination row: 128 B of values and the 16-byte granule of its 16 scales
+        static_assert(S::kScaleB == 16, "a bulk copy moves multiples of 16 bytes");
         auto put = [&](char* dst) {
           bulk_store(dst + voff, my_piece, S::kValueB);
-          if constexpr (S::kScaleB == 16) {
-            bulk_store(dst + soff, my_piece + S::kValueB, 16);
-          } else {
-            *reinterpret_cast<uint2*>(dst + soff) = *reinterpret_cast<const uint2*>(my_piece + S::kValueB);
-          }
+          bulk_store(dst + soff, my_piece + S::kValueB, 16);
         };
         if (p.local_q) put(p.local_q + (size_t)row * qrow_bytes);
         if (p.nranks) {
@@ -355,15 +358,6 @@ static StatusWords* gemm_status_word() {
 
 using namespace fp4ar;
 
-// 0 = automatic (currently always 256), 128 or 256 = forced.  The 128-wide shape is selectable but not the default
-// until it has been timed against the 256-wide one on the target machine.
-static int g_gemm_tile_n = 0;
-extern "C" int fp4ar_gemm_set_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256) return FP4AR_ERR_ARGUMENT;
-  g_gemm_tile_n = bn;
-  return FP4AR_OK;
-}
-
 template <int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmShape<BN>;
@@ -377,7 +371,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, const void* wt, int M, int N,
                                 int K, float gs, void* local_q, float* dbg_acc, fp4ar_stream stream) {
-  const int bn = g_gemm_tile_n == 128 ? 128 : 256;
+  constexpr int bn = 256;
   if (!x || !wt || M < 1 || N < bn || K < kBK || (N % bn) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
   if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
@@ -406,7 +400,7 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   p.timeout_ns = 2000000000ull;
   CUtensorMap ma, mb;
   if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, bn)) return FP4AR_ERR_UNSUPPORTED;
-  return bn == 128 ? launch_gemm<128>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256>(ma, mb, p, (cudaStream_t)stream);
+  return launch_gemm<bn>(ma, mb, p, (cudaStream_t)stream);
 }
 
 extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {

@@ -68,39 +68,26 @@ static std::vector<ArKernelEntry>& kernel_table() {
     ar_register_p1(buf, &n); ar_register_p2(buf, &n); ar_register_p2b(buf, &n);
     ar_register_p4(buf, &n); ar_register_p4b(buf, &n); ar_register_p8(buf, &n); ar_register_p8b(buf, &n);
     ar_register_cmp(buf, &n);
-    ar_register_t6(buf, &n);
-    ar_register_t6x4(buf, &n);
-    ar_register_cold(buf, &n);
+    ar_register_t6p4(buf, &n); ar_register_t6p4b(buf, &n); ar_register_t6p8(buf, &n); ar_register_t6p8b(buf, &n);
     table.assign(buf, buf + n);
   });
   return table;
 }
-static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi, int T, int variant = 0) {
+static const ArKernelEntry* find_kernel(int P, int algo, int input, int epi, int T) {
   for (const ArKernelEntry& e : kernel_table())
-    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi && e.T == T && e.variant == variant) return &e;
+    if (e.P == P && e.algo == algo && e.input == input && e.epi == epi && e.T == T) return &e;
   return nullptr;
 }
-// Experimental kernel builds: bits 8-15 of tune[1] if set, else FP4AR_KERNEL_VARIANT from the environment, else 0 (the
-// product kernels).  A shape that the variant does not provide falls back to the product kernel.
-static int kernel_variant_for(const fp4ar_args& a) {
-  const int from_call = (a.tune[1] >> 8) & 255;
-  if (from_call) return from_call;
-  static const int from_env = [] {
-    const char* s = std::getenv("FP4AR_KERNEL_VARIANT");
-    const int v = s ? std::atoi(s) : 0;
-    return v > 0 && v < 256 ? v : 0;
-  }();
-  return from_env;
-}
-// Team width: tune[2] of the call if set, else FP4AR_TEAM_WARPS from the environment, else the default.
-static int team_warps_for(const fp4ar_args& a) {
+// Team width: tune[2] of the call if set, else FP4AR_TEAM_WARPS from the environment (a preference: shapes that are
+// not compiled at that width use their default), else the default of the shape.
+static int team_warps_for(const fp4ar_args& a, int nranks, int algo) {
   if (a.tune[2] > 0) return a.tune[2];
   static const int from_env = [] {
     const char* s = std::getenv("FP4AR_TEAM_WARPS");
     const int v = s ? std::atoi(s) : 0;
-    return v > 0 ? v : kDefaultTeamWarps;
+    return v > 0 ? v : 0;
   }();
-  return from_env;
+  return from_env > 0 ? from_env : default_team_warps(nranks, algo);
 }
 
 #ifdef FP4AR_PHASE_TIMERS
@@ -267,10 +254,11 @@ extern "C" const char* fp4ar_last_cuda_error(void) {
   return copy.c_str();
 }
 
-extern "C" int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps, int variant) {
-  const ArKernelEntry* e = find_kernel(nranks, algo, input, epilogue, team_warps, variant);
+extern "C" int fp4ar_has_kernel(int nranks, int algo, int input, int epilogue, int team_warps) {
+  const ArKernelEntry* e = find_kernel(nranks, algo, input, epilogue, team_warps);
   return e && e->fn ? e->max_teams : 0;
 }
+extern "C" int fp4ar_default_team_warps(int nranks, int algo) { return default_team_warps(nranks, algo); }
 
 extern "C" const char* fp4ar_build_info(void) {
   static std::string s;
@@ -301,14 +289,10 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   if (algo == FP4AR_ALGO_AUTO) algo = c->nranks <= 2 ? FP4AR_ALGO_ONESHOT : FP4AR_ALGO_TWOSHOT;
   if (algo != FP4AR_ALGO_ONESHOT && algo != FP4AR_ALGO_TWOSHOT) return FP4AR_ERR_ARGUMENT;
   if (c->nranks == 1) algo = FP4AR_ALGO_ONESHOT;
-  const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, team_warps_for(a0));
-  // a team width that comes from the environment is a preference: shapes not compiled at that width use the default
-  if (!ke && a0.tune[2] <= 0) ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, kDefaultTeamWarps);
+  const ArKernelEntry* ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, team_warps_for(a0, c->nranks, algo));
+  // a team width that comes from the environment is a preference: shapes not compiled at that width use their default
+  if (!ke && a0.tune[2] <= 0) ke = find_kernel(c->nranks, algo, a0.input, a0.epilogue, default_team_warps(c->nranks, algo));
   if (!ke) return FP4AR_ERR_UNSUPPORTED;
-  if (const int variant = kernel_variant_for(a0)) {
-    const ArKernelEntry* kv = find_kernel(c->nranks, algo, a0.input, a0.epilogue, ke->T, variant);
-    if (kv) ke = kv;
-  }
 
   ArParams prm;
   std::memset(&prm, 0, sizeof(prm));

@@ -4,7 +4,7 @@ CUDA events around the replay, per-iteration maximum over ranks, median / p10 / 
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         -m fp4_all_reduce_b200.harness.bench_cli --rows 1024,16384 --modes fused,xport,compute,empty \
-        --inputs bf16,nvfp4 --epilogues 0,1 [--algos auto] [--team-warps 2,3] [--teams 0] [--graph 10] \
+        --inputs bf16,nvfp4 --epilogues 0,1 [--algos auto] [--team-warps 3,6] [--teams 0] [--graph 10] \
         [--iters 50] [--warmup 10] [--nccl] [--out timing.jsonl]
 
 (also runs as a plain `python -m ...` on one GPU: a one-rank context.)
@@ -63,13 +63,10 @@ class Cell:
         self.outq = torch.empty(rows, nb, dtype=torch.uint8, device=dev) if epi >= 2 else None
         self.rows, self.kind, self.epi = rows, kind, epi
 
-    variant = 0
-
     def args(self, i, mode, algo, teams, tw, rows=None, lags=0):
         return make_args(x=self.xs[i % self.nsets], out=self.out, rows=self.rows if rows is None else rows, mode=mode,
                          algo=algo, input=self.kind, epilogue=self.epi, gs=self.gs, res_in=self.res, res_out=self.res,
-                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw, lags=lags,
-                         variant=self.variant)
+                         weight=self.w, outq=self.outq, qscale=168.0, teams=teams, team_warps=tw, lags=lags)
 
 
 def main(argv=None) -> int:
@@ -82,7 +79,6 @@ def main(argv=None) -> int:
     ap.add_argument("--team-warps", default="0")
     ap.add_argument("--teams", default="0")
     ap.add_argument("--lags", default="0", help="two-shot depths, comma list of lag_owner+16*lag_finish (e.g. 33 = 1,2; 50 = 2,3; 66 = 2,4)")
-    ap.add_argument("--variant", type=int, default=0, help="experimental kernel build (0 = product kernels)")
     ap.add_argument("--graph", type=int, default=10)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
@@ -90,6 +86,7 @@ def main(argv=None) -> int:
     ap.add_argument("--nccl-only", action="store_true", help="skip the fused-kernel cells (NCCL sweeps)")
     ap.add_argument("--nccl-reg", action="store_true",
                     help="also time NCCL on buffers allocated with ncclMemAlloc and registered with the communicator")
+    ap.add_argument("--timeout-ms", type=int, default=2000, help="device-side wait limit of the context")
     ap.add_argument("--tag", default="")
     ap.add_argument("--out", default=None)
     ns = ap.parse_args(argv)
@@ -104,6 +101,16 @@ def main(argv=None) -> int:
     rank = dist.get_rank() if world > 1 else 0
     rows_list = [int(r) for r in ns.rows.split(",")]
     ctx = Fp4ArContext(max(rows_list), device=dev)
+    ctx.set_timeout_ms(ns.timeout_ms)
+
+    def rearm_if_failed():
+        """A wait that gave up on ANY rank leaves slots un-armed everywhere: decide together, reset together."""
+        code = torch.tensor([int(ctx.status().code != 0)], dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_reduce(code)
+        if int(code.item()) != 0:
+            ctx.reset()
+
     common = {"kind": "timing", "tp": world, "hidden": N.HIDDEN, "graphK": ns.graph, "iters": ns.iters,
               "warmup": ns.warmup, "tag": ns.tag, **run_info(dev)}
     records = []
@@ -127,7 +134,6 @@ def main(argv=None) -> int:
         for inp in ns.inputs.split(","):
             for epi in (int(e) for e in ns.epilogues.split(",")):
                 cell = Cell(rows, INPUTS[inp], epi, rank, world, dev)
-                cell.variant = ns.variant
                 for algo in ([] if ns.nccl_only else ns.algos.split(",")):
                     for tw in (int(t) for t in ns.team_warps.split(",")):
                         for teams, lags in ((int(t), int(l)) for t in ns.teams.split(",") for l in ns.lags.split(",")):
@@ -141,12 +147,13 @@ def main(argv=None) -> int:
                                 res[mode] = t["med_us"]
                                 st = ctx.status()
                                 emit({**common, "variant": "fp4ar", "mode": mode, "algo": algo, "rows": rows,
-                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags, "kernel_variant": ns.variant,
+                                      "input": inp, "epilogue": epi, "team_warps": tw, "teams": teams, "lags": lags,
                                       "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
                                       "p90_us": round(t["p90_us"], 3), "rank_med_us": t.get("rank_med_us"),
                                       "sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons"), "status": st.describe(),
                                       "wire_gbs": round(rows * 3460 * (1 if world <= 2 else 2 * (world - 1) / world) /
                                                         t["med_us"] / 1e3, 1) if world > 1 else None})
+                                rearm_if_failed()
                             if all(k in res for k in ("fused", "xport", "compute", "empty")):
                                 F, X, Cc, E = res["fused"], res["xport"], res["compute"], res["empty"]
                                 den = min(X - E, Cc - E)

@@ -47,7 +47,6 @@ class CellConfig:
     qscale: float = 168.0
     teams: int = 0
     lags: int = 0                  # two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default)
-    variant: int = 0               # experimental kernel build (0 = product kernels)
     team_warps: int = 0            # warps per row team (0 = default)
 
     def resolved_algo(self) -> int:
@@ -140,7 +139,7 @@ class Outputs:
 def args_for(cfg: CellConfig, inp: InputSet, outs: Outputs, local: int, rank: int, mode=N.MODE_FUSED) -> N.Args:
     return make_args(x=inp.xs[rank], out=outs.out[local], rows=cfg.rows, mode=mode, algo=cfg.algo, input=cfg.input,
                      epilogue=cfg.epilogue, gs=inp.gs, res_in=inp.res, res_out=outs.res_out[local], weight=inp.weight,
-                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags, variant=cfg.variant,
+                     eps=cfg.eps, weight_bias=cfg.weight_bias, outq=outs.outq[local], qscale=cfg.qscale, teams=cfg.teams, lags=cfg.lags,
                      team_warps=cfg.team_warps)
 
 

@@ -45,10 +45,8 @@ def main(argv=None) -> int:
     ap.add_argument("--ms", dest="m", default="1024,4096,16384")
     ap.add_argument("--tp", default="2,4,8")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--tile-n", type=int, default=0, help="force the GEMM's output-tile width (128 or 256; 0 = automatic)")
     ns = ap.parse_args(argv)
     torch.cuda.set_device(0)
-    G.set_tile_n(ns.tile_n)
     peak, kind = _peak()
     Nn = 6144
     for tp in (int(t) for t in ns.tp.split(",")):
@@ -65,7 +63,7 @@ def main(argv=None) -> int:
             print(json.dumps({"op": "gemm_nvfp4", "M": M, "K": K, "N": Nn, "tp": tp, "us": round(us_ours, 1),
                               "tflops": round(fl / us_ours / 1e6, 1), "frac_of_cublas_bf16": round(fl / us_ours / 1e6 / peak, 3),
                               "cublas_bf16_us": round(us_ref, 1), "cublas_tflops": round(fl / us_ref / 1e6, 1),
-                              "peak_kind": kind, "tile_n": ns.tile_n or 256, "status": G.gemm_status().code}), flush=True)
+                              "peak_kind": kind, "tile_n": 256, "status": G.gemm_status().code}), flush=True)
     return 0
 
 

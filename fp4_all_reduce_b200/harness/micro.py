@@ -14,7 +14,9 @@
   flag) -> GB/s versus tile size; and nanoseconds per (remote 16-byte store + fence.acq_rel.sys) from one thread.
 * tear: are 16-byte stores into a peer seen whole?  Rank 0 rewrites 4096 slots of rank 1 with {i,i,i,i} while rank 1
   polls them; counts loads whose words differ, for 16-byte and (the control) 2 x 8-byte accesses.
-* copy engine: torch `copy_` between the symmetric buffers (cudaMemcpyAsync peer copy) against the SM kernels.
+* copy engine: a peer copy issued by the runtime (cudaMemcpyAsync) against the SM kernels.
+* link counters: `nvidia-smi nvlink -gt d` read before and after a run of bulk stores and of st.v4 stores: counted
+  bytes over payload bytes (read-only; skipped with a record when the counters are not exposed).
 
 One JSON line per configuration (GB/s of payload per direction per GPU; time = CUDA events, max over ranks).
 The reference's equivalents: bench/micro/bw.cu, lat.cu, fence.cu, tear.cu, bench/link/ce.cu and their README
@@ -33,6 +35,28 @@ import torch.distributed as dist
 
 from .. import _native as N
 from ..parallel.symmetric import allocate_symmetric, multicast_pointer
+
+
+def nvlink_data_kib(index: int):
+    """(tx KiB, rx KiB) summed over the links of GPU `index`, read from `nvidia-smi nvlink -gt d`; None when the
+    tool or the counters are not available.  Reading counters changes nothing on the GPU.  (The reference brackets its
+    runs the same way: bench/link/common.sh:5-6, cnt.py.)"""
+    import re
+    import shutil
+    import subprocess
+
+    exe = shutil.which("nvidia-smi")
+    if exe is None:
+        return None
+    try:
+        out = subprocess.run([exe, "nvlink", "-gt", "d", "-i", str(index)], capture_output=True, text=True, timeout=20).stdout
+    except Exception:
+        return None
+    tx = [int(v) for v in re.findall(r"Data Tx:\s*(\d+)\s*KiB", out)]
+    rx = [int(v) for v in re.findall(r"Data Rx:\s*(\d+)\s*KiB", out)]
+    if not tx or not rx:
+        return None
+    return sum(tx), sum(rx)
 
 
 def main(argv=None) -> int:
@@ -98,6 +122,27 @@ def main(argv=None) -> int:
             moved = (total // chunk) * chunk
             emit({"kind": "bw", "method": names[method], "chunk": chunk, "ctas": ctas, "inflight": inflight, "active": active,
                   "tp": world, "mb": ns.mb, "ms": round(ms, 4), "gbs_per_dir": round(moved / ms / 1e6, 1)})
+    # wire bytes against payload bytes from the link counters (256-byte bulk-store packets against 128-byte st.v4 ones)
+    for method, chunk in ((0, 4096), (1, 4096)):
+        torch.cuda.synchronize()
+        dist.barrier()
+        before = nvlink_data_kib(local) if rank == 0 else None
+        reps = 8
+        for _ in range(reps):
+            N.check(lib.fp4ar_micro_bandwidth(ptrs[nxt], total, chunk, method, 148, 4 if method == 0 else 1, stream()), "micro_bw")
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            after = nvlink_data_kib(local)
+            if before is None or after is None:
+                emit({"kind": "nvlink_counters", "method": names[method], "skipped": "nvidia-smi nvlink counters not available"})
+            else:
+                payload = reps * (total // chunk) * chunk
+                tx = (after[0] - before[0]) * 1024
+                rx = (after[1] - before[1]) * 1024
+                emit({"kind": "nvlink_counters", "method": names[method], "chunk": chunk, "payload_bytes_sent": payload,
+                      "counter_tx_bytes": tx, "counter_rx_bytes": rx, "tx_over_payload": round(tx / payload, 4) if payload else None})
+
     def timed(launch, active):
         """min over iterations of the CUDA-event time of `launch`, max over ranks."""
         times = []

@@ -3,7 +3,8 @@
     python -m fp4_all_reduce_b200.harness.ops_bench [--rows 16384] [--iters 20] [--ops encode,decode2,...]
 
 Each op is timed with CUDA events on its stream after 3 warm-up launches; a 512 MiB buffer is overwritten
-between timed launches so that no input is found in L2.  Bytes counted are the algorithmic ones (inputs read
+between timed launches so that no input is found in L2, and a short device-side sleep before the first event lets
+the host enqueue the launch ahead of time, so the events bracket device time only.  Bytes counted are the algorithmic ones (inputs read
 once, outputs written once).  The denominator is `hbm_gbs` of MEASURED_PEAKS.json next to the repository
 root when present (a plain device copy measured on the same machine pool), else 6650 GB/s ("of fallback").
 The reference project's equivalent is bench/codec/codec_bench.cu:730-928 (copy roof + per-kernel times).
@@ -74,6 +75,7 @@ def main(argv=None) -> int:
         ts = []
         for _ in range(ns.iters):
             flush.fill_(1)
+            torch.cuda._sleep(400_000)   # the GPU idles ~0.2 ms while the host enqueues: launch overhead stays outside the events
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); fn(); b.record(); b.synchronize()
             ts.append(a.elapsed_time(b) * 1e3)

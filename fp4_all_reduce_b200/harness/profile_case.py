@@ -32,7 +32,6 @@ def main(argv=None) -> int:
     ap.add_argument("--calls", type=int, default=3)
     ap.add_argument("--teams", type=int, default=0)
     ap.add_argument("--team-warps", type=int, default=0)
-    ap.add_argument("--variant", type=int, default=0, help="kernel build variant (0 = product kernels)")
     ap.add_argument("--lags", type=int, default=0, help="two-shot pipeline depths, lag_owner + 16 * lag_finish (0 = default)")
     ap.add_argument("--solo", action="store_true",
                     help="create rank 0 of a --ranks group on this GPU and launch it alone (needs --mode 2: every push is looped back)")
@@ -57,7 +56,7 @@ def main(argv=None) -> int:
         return make_args(x=xs[r], out=outs[r] if ns.epilogue <= 1 else None, rows=rows, mode=ns.mode, algo=ns.algo,
                          input=ns.input, epilogue=ns.epilogue, gs=gs, res_in=res[r] if ns.epilogue else None,
                          res_out=res[r] if ns.epilogue else None, weight=w if ns.epilogue else None, outq=outq[r],
-                         qscale=168.0, teams=ns.teams, team_warps=ns.team_warps, variant=ns.variant, lags=ns.lags)
+                         qscale=168.0, teams=ns.teams, team_warps=ns.team_warps, lags=ns.lags)
 
     if ns.solo:
         if ns.mode != N.MODE_COMPUTE:
@@ -82,7 +81,7 @@ def main(argv=None) -> int:
         times.append(a.elapsed_time(b) * 1000.0)
     st = ctx.status()
     print(json.dumps({"ranks": P, "rows": rows, "epilogue": ns.epilogue, "input": ns.input, "mode": ns.mode,
-                      "team_warps": ns.team_warps, "variant": ns.variant, "lags": ns.lags, "solo": bool(ns.solo),
+                      "team_warps": ns.team_warps, "lags": ns.lags, "solo": bool(ns.solo),
                       "us_per_call": [round(t, 2) for t in times], "status": st.describe(),
                       "ctas_per_rank": ctx.ctas_per_rank()}))
     ctx.close()

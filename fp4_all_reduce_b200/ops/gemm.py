@@ -88,11 +88,6 @@ def gemm_all_reduce_add_rms_norm(ctx, x: torch.Tensor, wt: torch.Tensor, gs: Seq
     return (o if o is not None else q), residual
 
 
-def set_tile_n(bn: int) -> None:
-    """Force the GEMM's output-tile width (128 or 256; 0 = automatic) for the following calls of this process."""
-    N.check(N.cuda().fp4ar_gemm_set_tile_n(int(bn)), "fp4ar_gemm_set_tile_n")
-
-
 def gemm_status() -> N.StatusWords:
     w = N.StatusWords()
     N.check(N.cuda().fp4ar_gemm_status(C.byref(w)), "fp4ar_gemm_status")

@@ -58,7 +58,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 def make_args(*, x=None, out=None, rows: int, mode=N.MODE_FUSED, algo=N.ALGO_AUTO, input=N.IN_BF16,
               epilogue=N.EPI_NONE, gs: Optional[Sequence[float]] = None, res_in=None, res_out=None, weight=None,
               eps: float = 1e-6, weight_bias: float = 1.0, outq=None, qscale: float = 1.0,
-              teams: int = 0, no_pdl: bool = False, team_warps: int = 0, lags: int = 0, variant: int = 0) -> N.Args:
+              teams: int = 0, no_pdl: bool = False, team_warps: int = 0, lags: int = 0) -> N.Args:
     a = N.Args()
     a.x = _ptr(x); a.out = _ptr(out)
     a.rows = rows; a.hidden = N.HIDDEN
@@ -68,7 +68,7 @@ def make_args(*, x=None, out=None, rows: int, mode=N.MODE_FUSED, algo=N.ALGO_AUT
     a.res_in = _ptr(res_in); a.res_out = _ptr(res_out); a.weight = _ptr(weight)
     a.eps = eps; a.weight_bias = weight_bias
     a.outq = _ptr(outq); a.qscale = qscale
-    a.tune[0] = teams; a.tune[1] = (1 if no_pdl else 0) | ((variant & 255) << 8); a.tune[2] = team_warps; a.tune[3] = lags
+    a.tune[0] = teams; a.tune[1] = 1 if no_pdl else 0; a.tune[2] = team_warps; a.tune[3] = lags
     return a
 
 

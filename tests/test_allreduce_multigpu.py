@@ -67,12 +67,10 @@ def test_fused_gemm_push_allreduce_matches_host_model(world):
     assert all(r.get("status", "ok") == "ok" for r in recs if r.get("kind") == "timing"), recs
 
 
-@pytest.mark.skipif(os.environ.get("FP4AR_RUN_UNVERIFIED") != "1",
-                    reason="comparison variants not yet verified on a GPU; set FP4AR_RUN_UNVERIFIED=1")
 def test_comparison_variants_match_host_model_on_two_gpus():
     if 2 not in _world_sizes():
         pytest.skip("needs 2 GPUs")
     rc, recs, log = _run_module(2, "compare_bench", ["--rows", "777", "--check", "--iters", "2", "--warmup", "1", "--graph", "3"], 29661)
     assert rc == 0, log
     checks = [r for r in recs if r.get("kind") == "check"]
-    assert len(checks) == 3 and all(r["pass"] for r in checks), checks
+    assert len(checks) == 8 and all(r["pass"] for r in checks), checks

@@ -1,7 +1,7 @@
-"""Flag-push and pull comparison variants on one GPU (ranks emulated as CTA groups of one cooperative launch):
-bit-identical to the one-shot host model, across calls (both buffers, generation counter), in a CUDA graph, and
-with a row count that is not a multiple of the tile."""
-import os
+"""The comparison variants (flag push, pull, pull with NVFP4 input, two-shot pull, pull + pushed all-gather) on one
+GPU (ranks emulated as CTA groups of one cooperative launch): bit-identical to the one-shot / two-shot host model,
+across calls (both buffers, generation counter), in a CUDA graph, and with a row count that is not a multiple of
+the tile."""
 
 import numpy as np
 import pytest
@@ -10,25 +10,24 @@ import torch
 from fp4_all_reduce_b200 import _native as N
 from fp4_all_reduce_b200 import oracle as O
 from fp4_all_reduce_b200.harness.gate import CellConfig, make_inputs
-from fp4_all_reduce_b200.parallel.compare import CompareEmulated
+from fp4_all_reduce_b200.parallel.compare import TWO_SHOT, CompareEmulated
 
-# These kernels were written after the last GPU session of their build and have not executed on a GPU yet; until
-# they have, they only run on request so that a fault in them cannot take the rest of the GPU suite down.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("FP4AR_RUN_UNVERIFIED") != "1",
-                                 reason="comparison variants not yet verified on a GPU; set FP4AR_RUN_UNVERIFIED=1")]
+pytestmark = pytest.mark.gpu
 
 
 def _mism(t, exp_bits):
     return int(np.count_nonzero(O.bf16_bits(t) != exp_bits))
 
 
-@pytest.mark.parametrize("variant", ["flag_push", "pull"])
+@pytest.mark.parametrize("variant", ["flag_push", "pull", "pull_nvfp4", "pull_twoshot", "pull_rs_push_ag"])
 @pytest.mark.parametrize("P", [1, 2, 4, 8])
 def test_compare_variant_matches_host_model(variant, P):
+    if variant in TWO_SHOT and P == 1:
+        pytest.skip("two-shot needs at least two ranks")
     dev = torch.device("cuda", 0)
     rows = 203                                   # not a multiple of 4: the last tile is ragged
-    cfg = CellConfig(nranks=P, rows=rows, algo=N.ALGO_ONESHOT, dist="mags")
+    cfg = CellConfig(nranks=P, rows=rows, algo=N.ALGO_TWOSHOT if variant in TWO_SHOT else N.ALGO_ONESHOT,
+                     input=N.IN_NVFP4 if variant == "pull_nvfp4" else N.IN_BF16, dist="mags")
     sets = [make_inputs(cfg, s, dev) for s in range(3)]
     grp = CompareEmulated(P, 256, dev)
     grp.timeout_ms = 300                       # a broken hand-off ends in seconds, not minutes
@@ -37,7 +36,7 @@ def test_compare_variant_matches_host_model(variant, P):
         s = sets[call % 3]
         for o in outs:
             o.zero_()
-        grp.all_reduce(variant, s.xs, outs)
+        grp.all_reduce(variant, s.xs, outs, gs=s.gs)
         torch.cuda.synchronize()
         assert grp.status().ok, grp.status().describe()
         for r in range(P):
@@ -45,17 +44,18 @@ def test_compare_variant_matches_host_model(variant, P):
     # a shorter call in between, then a captured graph of several calls
     short = [x[:57].contiguous() for x in sets[0].xs]
     souts = [torch.zeros(57, N.HIDDEN, dtype=torch.bfloat16, device=dev) for _ in range(P)]
-    grp.all_reduce(variant, short, souts)
+    grp.all_reduce(variant, short, souts, gs=sets[0].gs)
     torch.cuda.synchronize()
+    assert grp.status().ok, grp.status().describe()
     assert _mism(souts[0], sets[0].exp["out"][:57]) == 0
     st = torch.cuda.Stream()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.stream(st):
-        grp.all_reduce(variant, sets[1].xs, outs, stream=st)     # warm-up on the capture stream
+        grp.all_reduce(variant, sets[1].xs, outs, stream=st, gs=sets[1].gs)     # warm-up on the capture stream
         st.synchronize()
         with torch.cuda.graph(g, stream=st):
             for _ in range(3):
-                grp.all_reduce(variant, sets[2].xs, outs, stream=st)
+                grp.all_reduce(variant, sets[2].xs, outs, stream=st, gs=sets[2].gs)
     for _ in range(2):
         for o in outs:
             o.zero_()

@@ -67,23 +67,3 @@ def test_gemm_push_then_allreduce_on_emulated_ranks(P):
             assert np.array_equal(O.bf16_bits(outs[r]), exp["out"]), (call, r)
             assert np.array_equal(O.bf16_bits(res[r]), exp["res_out"]), (call, r)
     g.close()
-
-
-@pytest.mark.skipif(__import__("os").environ.get("FP4AR_RUN_UNVERIFIED") != "1",
-                    reason="128-wide GEMM tiles not yet verified on a GPU; set FP4AR_RUN_UNVERIFIED=1")
-@pytest.mark.parametrize("M,K,Nn", [(128, 64, 256), (300, 512, 512), (1024, 2048, 6144)])
-def test_gemm_128_wide_tiles(M, K, Nn):
-    """The selectable 128 x 128 tile shape gives the same accumulators and the same NVFP4 rows."""
-    x, wt = _xw(M, K, Nn, 3)
-    gs = G.calibrate_gs(x, wt)
-    G.set_tile_n(128)
-    try:
-        q, acc = G.gemm_nvfp4(x, wt, gs, want_acc=True)
-        torch.cuda.synchronize()
-    finally:
-        G.set_tile_n(0)
-    assert G.gemm_status().code == 0
-    ref = x.float() @ wt.float().t()
-    assert (acc - ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 1e-4
-    want = O.encode_static_f32(acc.cpu().numpy(), gs)
-    assert np.count_nonzero(q.cpu().numpy() != want) == 0

@@ -52,31 +52,23 @@ def test_window_bytes_and_argument_validation_without_a_gpu(cuda_lib):
     assert b"sm_100a" in lib.fp4ar_build_info()
 
 
-def test_kernel_table_holds_every_product_shape_and_the_selectable_builds(cuda_lib):
-    """Host-side check of the compiled-shape table (no GPU): every product shape is registered under variant 0, and
-    the selectable builds sit beside them without displacing them."""
-    from fp4_all_reduce_b200 import _native as N
-
+def test_kernel_table_holds_every_product_shape(cuda_lib):
+    """Host-side check of the compiled-shape table (no GPU): three-warp teams for every shape, six-warp teams for the
+    two-shot shapes of four and eight ranks (their default), nothing else."""
     lib = cuda_lib
     has = lambda *a: int(lib.fp4ar_has_kernel(*a))
-    for T in (2, 3):
-        for P, algos in ((1, (0,)), (2, (0, 1)), (4, (0, 1)), (8, (0, 1))):
-            for algo in algos:
-                assert has(P, algo, 0, 0, T, 0) > 0, (P, algo, T)
-        # the defaults of the four headline cells
-        for P in (2, 4, 8):
-            algo = 0 if P == 2 else 1
-            for inp in (0, 1, 2):
-                for epi in (0, 1, 2, 3):
-                    assert has(P, algo, inp, epi, T, 0) > 0, (P, algo, inp, epi, T)
-    for P in (4, 8):
-        for inp, epi in ((0, 0), (0, 1), (1, 0), (1, 1), (2, 1)):
-            assert has(P, 1, inp, epi, 6, 0) == 3          # six-warp teams: three per CTA
-            assert has(P, 1, inp, epi, 3, 1) > 0           # experimental build 1 (cold paths)
-            assert has(P, 1, inp, epi, 6, 2) == 4          # experimental build 2: four six-warp teams
-            assert has(P, 1, inp, epi, 3, 0) == 4          # ... and the product kernel is still the one at variant 0
-    assert has(1, 0, 0, 1, 6, 0) == 3 and has(2, 0, 0, 1, 6, 0) == 3 and has(2, 0, 2, 1, 6, 0) == 3
-    assert has(2, 1, 0, 0, 6, 0) == 0 and has(4, 1, 0, 0, 3, 7) == 0
+    for P, algos in ((1, (0,)), (2, (0, 1)), (4, (0, 1)), (8, (0, 1))):
+        for algo in algos:
+            assert has(P, algo, 0, 0, 3) > 0, (P, algo)
+    for P in (2, 4, 8):
+        algo = 0 if P == 2 else 1
+        for inp in (0, 1, 2):
+            for epi in (0, 1, 2, 3):
+                assert has(P, algo, inp, epi, 3) > 0, (P, algo, inp, epi)
+                assert has(P, algo, inp, epi, 6) == (3 if P >= 4 else 0), (P, algo, inp, epi)
+                assert has(P, algo, inp, epi, 2) == 0
+    assert has(4, 0, 0, 0, 6) == 0 and has(1, 0, 0, 1, 6) == 0
+    assert lib.fp4ar_default_team_warps(8, 1) == 6 and lib.fp4ar_default_team_warps(2, 0) == 3
 
 
 def _unbound_context(nranks=2, max_rows=64):
