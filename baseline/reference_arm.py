@@ -48,6 +48,8 @@ def check(tp: int, rows: int, input_kind: str = "bf16") -> int:
         for variant, algo in (("L2", 0), ("L2", 1), ("L4", 0), ("L4", 1)):
             if variant == "L4" and tp != 4:
                 continue
+            if input_kind == "nvfp4" and variant == "L2" and algo == 1:
+                continue        # the reference's L2 takes NVFP4 input for its one-shot path only (kernels/push/tp2_l2.cu:1031)
             rec = run_shim(["--tp", tp, "--variant", variant, "--rows", rows, "--algo", algo, "--graph", 2, "--iters", 3,
                             "--warmup", 1, "--in", pre, "--dump", pre, "--input", input_kind])
             if "unavailable" in rec:

@@ -79,6 +79,7 @@ def _compile_one(src: Path, hdr: str, force: bool, verbose: bool) -> tuple[Path,
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
     stamp_file.write_text(stamp)
+    (OBJ / (src.stem + ".ptxas")).write_text(r.stderr)     # kept per unit, so the resource log of an incremental build is complete
     if verbose:
         print(f"[build] {src.name}")
     return obj, r.stderr, True
@@ -104,9 +105,11 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-        if logs:
-            with open(LIB / "build_resources.log", "w") as f:
-                f.write("\n".join(logs))
+        with open(LIB / "build_resources.log", "w") as f:
+            for src in srcs:
+                unit = OBJ / (src.stem + ".ptxas")
+                if unit.exists():
+                    f.write(unit.read_text() + "\n")
     return out
 
 

@@ -91,7 +91,8 @@ int fp4ar_launch(fp4ar_ctx* ctx, const fp4ar_args* args, fp4ar_stream stream);
 
 /* Synchronous read of the device status block of a local rank. */
 int fp4ar_status(fp4ar_ctx* ctx, int local_rank, fp4ar_status_words* out);
-/* How long a device-side wait may last before it gives up (default 2000 ms). */
+/* How long a device-side wait may last before it gives up (default 10000 ms, or FP4AR_TIMEOUT_MS from the
+ * environment when the context is created). */
 int fp4ar_set_timeout_ms(fp4ar_ctx* ctx, int ms);
 /* Re-arm the whole local window and clear the status.  Collective: barrier before the next launch. */
 int fp4ar_reset(fp4ar_ctx* ctx);

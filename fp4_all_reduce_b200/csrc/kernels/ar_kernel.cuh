@@ -195,7 +195,25 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   mbar_init_fence();
   fence_smem_to_async();
   __syncthreads();
+  const int rb = (int)(((long long)cta * prm.rows) / G), re = (int)(((long long)(cta + 1) * prm.rows) / G);
+  const int nk = (re - rb > team) ? (re - rb - team + nteams - 1) / nteams : 0;
+  auto row_of = [&](int k) { return rb + team + nteams * k; };
   pdl_wait_prior_grids();
+  // ---- first loads: they need nothing from the call state, so they go out before it is read ----
+  if (leader && nk > 0) {
+    if (IN == 0) {
+      mbar_arrive_expect(xbar + 0, kRowBytes);
+      bulk_load(xb, io.x + (size_t)row_of(0) * kRowBytes, kRowBytes, xbar + 0);
+      if (nk > 1) {
+        mbar_arrive_expect(xbar + 1, kRowBytes);
+        bulk_load(xb + kRowBytes, io.x + (size_t)row_of(1) * kRowBytes, kRowBytes, xbar + 1);
+      }
+    } else if (IN == 1) {
+      mbar_arrive_expect(qbar + 0, kQRowBytes);
+      bulk_load(recs, io.x + (size_t)row_of(0) * kQRowBytes, kQRowBytes, qbar + 0);
+    }
+  }
+
   const uint32_t call = io.ctrl[cta];
   pdl_release_dependents();
 
@@ -210,10 +228,6 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
   auto rs_slot = [&](int src, int row) -> size_t { return ((size_t)src * capo + row / P) * kRecStride; };
   auto ag_slot = [&](int own, int row) -> size_t { return ((size_t)(P + own) * capo + row / P) * kRecStride; };
 
-  const int rb = (int)(((long long)cta * prm.rows) / G), re = (int)(((long long)(cta + 1) * prm.rows) / G);
-  const int nk = (re - rb > team) ? (re - rb - team + nteams - 1) / nteams : 0;
-  auto row_of = [&](int k) { return rb + team + nteams * k; };
-  const int in_row_bytes = IN == 0 ? kRowBytes : kQRowBytes;
   int red_phase = 0;
 
   // Exchange one float per (warp, j) across the team: every lane returns with all six group values.
@@ -228,21 +242,6 @@ __global__ void __launch_bounds__(32 * T * ArShape<P, ALGO, IN, EPI, T>::kMaxTea
 #pragma unroll
     for (int g = 0; g < 6; g++) all6[g] = slot[g];
   };
-
-  // ---- first loads ----
-  if (leader && nk > 0) {
-    if (IN == 0) {
-      mbar_arrive_expect(xbar + 0, kRowBytes);
-      bulk_load(xb, io.x + (size_t)row_of(0) * kRowBytes, kRowBytes, xbar + 0);
-      if (nk > 1) {
-        mbar_arrive_expect(xbar + 1, kRowBytes);
-        bulk_load(xb + kRowBytes, io.x + (size_t)row_of(1) * kRowBytes, kRowBytes, xbar + 1);
-      }
-    } else if (IN == 1) {
-      mbar_arrive_expect(qbar + 0, kQRowBytes);
-      bulk_load(recs, io.x + (size_t)row_of(0) * kQRowBytes, kQRowBytes, qbar + 0);
-    }
-  }
 
   // =============================================================================================
   // Row completion shared by every algorithm: `fill(j, acc)` produces the FP32 sum of pair j in slot

@@ -153,6 +153,11 @@ struct SrcList {
   float gs[kMaxRanksOps];
 };
 
+// Rows whose loads a team issues together before the first use (bytes in flight against registers).
+__host__ __device__ constexpr int decode_rows_per_trip(int ns, bool reenc) {
+  return ns == 1 ? 4 : (ns == 2 ? 2 : (reenc && ns <= 4 ? 2 : 1));
+}
+
 template <int NS, bool REENC>
 __global__ void __launch_bounds__(kTeamThreads, (NS > 4 || REENC) ? 3 : 4)
 decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
@@ -161,7 +166,7 @@ decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, p = threadIdx.x;
   uint8_t* stage = stage_all + warp * kStageBytes;
   int phase = 0;
-  constexpr int U = NS == 1 ? 4 : (NS == 2 ? 2 : 1);
+  constexpr int U = decode_rows_per_trip(NS, REENC);
   for (int row0 = blockIdx.x * U; row0 < rows; row0 += gridDim.x * U) {
     uint4 q[U][NS];
     uint32_t sf[U][NS];
@@ -342,8 +347,7 @@ static int launch_decode(int nsrc, const void* const* src, long pitch, const flo
     if (!sl.rs[s]) { if (!gs) return FP4AR_ERR_ARGUMENT; sl.gs[s] = gs[s]; }
   }
   if (rows == 0) return FP4AR_OK;
-  const int per_trip = nsrc == 1 ? 4 : (nsrc == 2 ? 2 : 1);
-  const int grid = team_grid(rows, per_trip, (nsrc > 4 || REENC) ? 3 : 4);
+  const int grid = team_grid(rows, decode_rows_per_trip(nsrc, REENC), (nsrc > 4 || REENC) ? 3 : 4);
 #define FP4AR_DEC_CASE(N)                                                                                          \
   case N:                                                                                                          \
     decode_sum_kernel<N, REENC><<<grid, kTeamThreads, 0, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);       \

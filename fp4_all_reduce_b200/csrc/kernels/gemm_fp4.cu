@@ -8,7 +8,8 @@
 //                 where the AllReduce kernel in "pushed input" mode finds them, and/or
 //               - into a local [M, N/2 + N/16] NVFP4 tensor.
 //
-// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.
+// sm_100a structure: persistent CTAs (one per SM), 128 x 256 or 128 x 192 output tiles (whichever fills the last wave
+// of the 148 CTAs better), K in blocks of 64.
 //   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
 //                              128-byte swizzle, completion on mbarriers
 //   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
@@ -24,6 +25,7 @@
 // with a copy (README.md:76, docs/INTEGRATION.md:67-74, harness/fp4ar_bench.cu:205-215).
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include "../include/fp4ar.h"
@@ -40,16 +42,18 @@ constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
 
-// Tile width BN = 256 with a 4-stage ring.  (A 128-wide tile with a 6-stage ring, which doubles the number of tiles
-// for small M, was measured 15-35 % slower at every M from 1024 to 4096 and is not built.)
+// Tile width BN: 256 with a 4-stage ring, or 192 with a 5-stage ring.  With 148 persistent CTAs the tile count decides
+// how full the last wave is: M = 1024, N = 6144 gives 192 tiles of 128 x 256 (1.3 waves, 65 % busy) but 256 tiles of
+// 128 x 192 (1.7 waves, 86 % busy).  (A 128-wide tile with a 6-stage ring was measured 15-35 % slower at every M from
+// 1024 to 4096 and is not built.)
 template <int BN>
 struct GemmShape {
-  static_assert(BN == 256, "tile width");
-  static constexpr int kStages = 4;
-  static constexpr int kBBytes = BN * kBK * 2;                  // 32 KB / 16 KB
-  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 32 KB
-  static constexpr int kValueB = BN / 2, kScaleB = BN / 16;     // 128 + 16 B / 64 + 8 B of one row of one tile
-  static constexpr int kPieceBytes = (kValueB + kScaleB + 15) & ~15;   // 144 / 80: keeps every piece 16-byte aligned
+  static_assert(BN == 256 || BN == 192, "tile width");
+  static constexpr int kStages = BN == 256 ? 4 : 5;
+  static constexpr int kBBytes = BN * kBK * 2;                  // 32 KB / 24 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 40 KB
+  static constexpr int kValueB = BN / 2, kScaleB = BN / 16;     // 128 + 16 B / 96 + 12 B of one row of one tile
+  static constexpr int kPieceBytes = (kValueB + kScaleB + 15) & ~15;   // 144 / 112: keeps every piece 16-byte aligned
   static constexpr int kEpiBytes = kBM * kPieceBytes;
   static constexpr int kSmem = kStages * kStageBytes + kEpiBytes + 256 + 1024;   // + barriers + alignment slack
   // Instruction descriptor: D = F32, A = B = BF16, both K-major, N = BN, M = 128.
@@ -290,11 +294,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       fence_smem_to_async();
       if (row < p.M) {
         const size_t voff = (size_t)(n0 / 2), soff = (size_t)(p.N / 2 + n0 / 16);
-        // one row piece to one destination row: 128 B of values and the 16-byte granule of its 16 scales
-        static_assert(S::kScaleB == 16, "a bulk copy moves multiples of 16 bytes");
+        // one row piece to one destination row: the values by a bulk store; the scales by a bulk store when they are
+        // a 16-byte granule (BN = 256), else (12 bytes at a 4-byte aligned offset) by three word stores from registers
         auto put = [&](char* dst) {
           bulk_store(dst + voff, my_piece, S::kValueB);
-          bulk_store(dst + soff, my_piece + S::kValueB, 16);
+          if constexpr (S::kScaleB == 16) {
+            bulk_store(dst + soff, my_piece + S::kValueB, 16);
+          } else {
+            const uint32_t* sw = reinterpret_cast<const uint32_t*>(my_piece + S::kValueB);
+            uint32_t* dw = reinterpret_cast<uint32_t*>(dst + soff);
+#pragma unroll
+            for (int i = 0; i < S::kScaleB / 4; i++) dw[i] = sw[i];
+          }
         };
         if (p.local_q) put(p.local_q + (size_t)row * qrow_bytes);
         if (p.nranks) {
@@ -371,12 +382,23 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, const void* wt, int M, int N,
                                 int K, float gs, void* local_q, float* dbg_acc, fp4ar_stream stream) {
-  constexpr int bn = 256;
-  if (!x || !wt || M < 1 || N < bn || K < kBK || (N % bn) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
+  if (!x || !wt || M < 1 || N < 256 || K < kBK || (N % 256) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
   if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
-  // rows of the local NVFP4 tensor are 9N/16 bytes apart and are written with 16-byte bulk stores
-  if (local_q && (N % 256)) return FP4AR_ERR_ARGUMENT;
+  // Tile width: the one whose tiles keep the persistent CTAs busier over all waves; a 192-wide tile does about 4 %
+  // less work per cycle (more operand bytes per FLOP), and needs N to be a multiple of 192 as well.
+  int bn = 256;
+  {
+    const char* force = std::getenv("FP4AR_GEMM_TILE_N");
+    const int sms = device_sm_count();
+    auto busy = [&](int w) {
+      const long tiles = (long)(N / w) * ((M + kBM - 1) / kBM);
+      return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
+    };
+    if (N % 192 == 0 && 0.96 * busy(192) > busy(256)) bn = 192;
+    if (force && std::atoi(force) == 256) bn = 256;
+    if (force && std::atoi(force) == 192 && N % 192 == 0) bn = 192;
+  }
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.inv_gs = 1.0f / gs;
@@ -400,7 +422,7 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   p.timeout_ns = 2000000000ull;
   CUtensorMap ma, mb;
   if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, bn)) return FP4AR_ERR_UNSUPPORTED;
-  return launch_gemm<bn>(ma, mb, p, (cudaStream_t)stream);
+  return bn == 192 ? launch_gemm<192>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256>(ma, mb, p, (cudaStream_t)stream);
 }
 
 extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {

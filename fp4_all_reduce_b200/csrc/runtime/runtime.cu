@@ -165,7 +165,12 @@ static int create_common(fp4ar_ctx** out, int rank, int nranks, int device, int 
   c->emulated = emulated; c->nlocal = emulated ? nranks : 1;
   c->geo = geometry(max_rows, nranks);
   c->window_bytes = window_bytes;
-  c->timeout_ns = 2000ull * 1000000ull;
+  {
+    // how long a device-side wait may last: 10 s unless FP4AR_TIMEOUT_MS or fp4ar_set_timeout_ms says otherwise
+    const char* e = std::getenv("FP4AR_TIMEOUT_MS");
+    const long ms = e ? std::atol(e) : 0;
+    c->timeout_ns = (unsigned long long)(ms > 0 ? ms : 10000) * 1000000ull;
+  }
   for (int r = 0; r < nranks; r++) c->win[r] = (char*)windows[r];
   int sms = 0;
   FP4AR_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));

@@ -68,15 +68,27 @@ class InputSet:
     exp_dev: dict = field(default_factory=dict)  # the same outputs on the device (bit patterns), for the compares
 
 
+_GEN_CACHE: dict = {}
+
+
 def _gen(cfg: CellConfig, rank: int, set_id: int) -> torch.Tensor:
+    """One rank's BF16 partial of one input set.  Cells of a gate run that differ only in input kind or epilogue use
+    the same partials, so the generated tensors are kept (for one row count and distribution at a time)."""
+    key = (cfg.dist, cfg.rows, rank, set_id)
+    if key in _GEN_CACHE:
+        return _GEN_CACHE[key]
+    if _GEN_CACHE and next(iter(_GEN_CACHE))[:2] != key[:2]:
+        _GEN_CACHE.clear()
     if cfg.dist == "partial":
-        return D.partial(cfg.rows, rank, seed_offset=set_id)
-    if cfg.dist == "mags":
-        return D.gaussian_mags(cfg.rows, rank, set_id)
-    if cfg.dist == "special":
+        x = D.partial(cfg.rows, rank, seed_offset=set_id)
+    elif cfg.dist == "mags":
+        x = D.gaussian_mags(cfg.rows, rank, set_id)
+    elif cfg.dist == "special":
         x = D.special_rows(cfg.rows, rank + 3 * set_id)
-        return x
-    raise ValueError(cfg.dist)
+    else:
+        raise ValueError(cfg.dist)
+    _GEN_CACHE[key] = x
+    return x
 
 
 def make_inputs(cfg: CellConfig, set_id: int, device) -> InputSet:

@@ -27,17 +27,53 @@ from .. import _native as N
 from .. import oracle as O
 from ..parallel.context import Fp4ArContext
 from ..utils.runinfo import sources_digest
-from .gate import CellConfig, Outputs, args_for, make_inputs, mismatches, rel_l2
+from .gate import CellConfig, InputSet, Outputs, args_for, make_inputs, mismatches, rel_l2
 
 IN_NAMES = {"bf16": N.IN_BF16, "nvfp4": N.IN_NVFP4}
 ALGO_NAMES = {"auto": N.ALGO_AUTO, "oneshot": N.ALGO_ONESHOT, "twoshot": N.ALGO_TWOSHOT}
+
+
+def make_inputs_shared(cfg: CellConfig, dev, rank: int, world: int) -> list:
+    """The three input sets of a cell, each built (inputs + host model) by ONE rank and handed to the others over the
+    process group: the host model is the expensive part of a gate cell, and P ranks evaluating the same model on the
+    same cores would multiply its cost by P while the GPUs idle."""
+    builder = [s % world for s in range(3)]
+    mine = {s: make_inputs(cfg, s, dev) for s in range(3) if builder[s] == rank}
+    keys = (["out"] if cfg.epilogue <= 1 else ["outq"]) + (["res_out"] if cfg.epilogue >= 1 else [])
+    width = {"out": N.HIDDEN, "res_out": N.HIDDEN, "outq": N.QROW_BYTES if cfg.epilogue == 2 else N.MXROW_BYTES}
+    sets = []
+    for s in range(3):
+        src = builder[s]
+        inp = mine.get(s)
+        box = [inp.gs if inp is not None else None]
+        dist.broadcast_object_list(box, src=src)
+        gs = box[0]
+        if inp is None:
+            in_dtype, in_cols = (torch.bfloat16, N.HIDDEN) if cfg.input == N.IN_BF16 else (torch.uint8, N.QROW_BYTES)
+            xs = [torch.empty(cfg.rows, in_cols, dtype=in_dtype, device=dev) for _ in range(world)]
+            res = torch.empty(cfg.rows, N.HIDDEN, dtype=torch.bfloat16, device=dev) if cfg.epilogue else None
+            weight = torch.empty(N.HIDDEN, dtype=torch.bfloat16, device=dev) if cfg.epilogue else None
+            exp_dev = {k: torch.empty(cfg.rows, width[k], dtype=torch.int16 if k != "outq" else torch.uint8, device=dev)
+                       for k in keys}
+            inp = InputSet(xs, gs, res, weight, {}, None, exp_dev)
+        # as bytes: the expectations are 16-bit integer patterns, a type NCCL does not move
+        for t in inp.xs:
+            dist.broadcast(t.view(torch.uint8), src=src)
+        if cfg.epilogue:
+            dist.broadcast(inp.res.view(torch.uint8), src=src)
+            dist.broadcast(inp.weight.view(torch.uint8), src=src)
+        for k in keys:
+            dist.broadcast(inp.exp_dev[k].view(torch.uint8), src=src)
+        sets.append(inp)
+    torch.cuda.synchronize()
+    return sets
 
 
 def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int, graph_reps: int, skew_reps: int,
               skew_us: float, negctl: str | None, percall: int = 0) -> dict:
     dev = ctx.device
     rank, world = ctx.rank, ctx.nranks
-    sets = [make_inputs(cfg, s, dev) for s in range(3)]
+    sets = make_inputs_shared(cfg, dev, rank, world)
     outs = Outputs(cfg, dev, 1)
 
     launch_cfg = dataclasses.replace(cfg, weight_bias=cfg.weight_bias + 2.0 ** -7) if negctl == "bias" else cfg
@@ -73,7 +109,7 @@ def gate_cell(ctx: Fp4ArContext, cfg: CellConfig, *, reps: int, graph_calls: int
         rec["ranks_with_error"] = total(int(st.code != 0))
         rec["pass"] = False
         return rec
-    if cfg.epilogue == N.EPI_NONE:
+    if cfg.epilogue == N.EPI_NONE and rank == 0:      # rank 0 built set 0 and holds its exact FP32 sum
         rec["rel_l2_vs_fp32"] = rel_l2(sets[0], O.bf16_bits(outs.out[0]))
     first = outs.out[0] if outs.out[0] is not None else outs.outq[0]
     digest = torch.tensor([int(first.view(torch.uint8).to(torch.int64).sum().item())], dtype=torch.int64, device=dev)

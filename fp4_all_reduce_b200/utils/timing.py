@@ -32,6 +32,7 @@ def capture(fn: Callable[[int], None], calls: int, device, warm_calls: int = 2) 
     st = torch.cuda.Stream(device=device)
     st.wait_stream(torch.cuda.current_stream(device))
     with torch.cuda.stream(st):
+        align_ranks(device)          # ranks may arrive seconds apart (host-side set-up); the device waits are bounded
         for i in range(warm_calls):
             fn(i)
         st.synchronize()
