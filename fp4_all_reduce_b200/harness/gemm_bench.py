@@ -34,6 +34,7 @@ def _time(fn, iters):
     torch.cuda.synchronize()
     ts = []
     for _ in range(iters):
+        torch.cuda._sleep(400_000)   # the GPU idles ~0.2 ms while the host enqueues: launch overhead stays outside the events
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(); fn(); b.record(); b.synchronize()
         ts.append(a.elapsed_time(b) * 1e3)
