@@ -256,15 +256,20 @@ __device__ __forceinline__ float absmax16(const float* f) {
 // slots 0,1 are the first 16-value block, slots 2,3 the second.  `scales(bm0, bm1, mult0, mult1)` turns the two
 // block maxima into the scale bytes (returned) and the value multipliers: pair_block_scales with a row's
 // inverse scale, or its table-driven form.
+// The form with the two block maxima given is for callers that already have them (for the row maximum).
 template <bool CANON, class Scales>
-__device__ __forceinline__ uint32_t encode_pair_f32(const float* f, Scales&& scales, uint4& q) {
+__device__ __forceinline__ uint32_t encode_pair_f32(const float* f, float bm0, float bm1, Scales&& scales, uint4& q) {
   float mult_a, mult_b;
-  const uint32_t sf2 = scales(absmax16(f), absmax16(f + 16), mult_a, mult_b);
+  const uint32_t sf2 = scales(bm0, bm1, mult_a, mult_b);
   q.x = quant_slot_f32<CANON>(f, mult_a);
   q.y = quant_slot_f32<CANON>(f + 8, mult_a);
   q.z = quant_slot_f32<CANON>(f + 16, mult_b);
   q.w = quant_slot_f32<CANON>(f + 24, mult_b);
   return sf2;
+}
+template <bool CANON, class Scales>
+__device__ __forceinline__ uint32_t encode_pair_f32(const float* f, Scales&& scales, uint4& q) {
+  return encode_pair_f32<CANON>(f, absmax16(f), absmax16(f + 16), scales, q);
 }
 
 __device__ __forceinline__ float absmax32(const float* f, float m) {

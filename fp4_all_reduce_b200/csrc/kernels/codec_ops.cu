@@ -153,13 +153,28 @@ struct SrcList {
   float gs[kMaxRanksOps];
 };
 
+#ifndef EXP_REENC_U
+#define EXP_REENC_U 2
+#endif
+#ifndef EXP_REENC_BLK
+#define EXP_REENC_BLK 3
+#endif
+#ifndef EXP_DEC8_BLK
+#define EXP_DEC8_BLK 3
+#endif
+#ifndef EXP_DEC8_CH
+#define EXP_DEC8_CH 8
+#endif
 // Rows whose loads a team issues together before the first use (bytes in flight against registers).
 __host__ __device__ constexpr int decode_rows_per_trip(int ns, bool reenc) {
-  return ns == 1 ? 4 : (ns == 2 ? 2 : (reenc && ns <= 4 ? 2 : 1));
+  return ns == 1 ? 4 : (ns == 2 ? 2 : (reenc && ns <= 4 ? EXP_REENC_U : 1));
+}
+__host__ __device__ constexpr int decode_blocks_per_sm(int ns, bool reenc) {
+  return reenc ? EXP_REENC_BLK : (ns > 4 ? EXP_DEC8_BLK : 4);
 }
 
 template <int NS, bool REENC>
-__global__ void __launch_bounds__(kTeamThreads, (NS > 4 || REENC) ? 3 : 4)
+__global__ void __launch_bounds__(kTeamThreads, decode_blocks_per_sm(NS, REENC))
 decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
   __shared__ __align__(128) uint8_t stage_all[kTeamWarps * kStageBytes];
   __shared__ float xchg[16];
@@ -168,20 +183,21 @@ decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
   int phase = 0;
   constexpr int U = decode_rows_per_trip(NS, REENC);
   for (int row0 = blockIdx.x * U; row0 < rows; row0 += gridDim.x * U) {
-    uint4 q[U][NS];
-    uint32_t sf[U][NS];
-    float rsv[U][NS];
+    constexpr int CH = (NS > 4 && U == 1) ? EXP_DEC8_CH : NS;     // sources loaded together
+    uint4 q[U][CH];
+    uint32_t sf[U][CH];
+    float rsv[U][CH];
+    auto load_batch = [&](int u, int row, int s0) {
 #pragma unroll
-    for (int u = 0; u < U; u++) {
-      const int row = row0 + u < rows ? row0 + u : rows - 1;     // clamped: the extra loads are discarded
-#pragma unroll
-      for (int s = 0; s < NS; s++) {
-        const char* r = src.base[s] + (size_t)row * pitch;
+      for (int s = 0; s < CH; s++) {
+        const char* r = src.base[s0 + s] + (size_t)row * pitch;
         q[u][s] = __ldcs(reinterpret_cast<const uint4*>(r + 16 * p));
         sf[u][s] = __ldcs(reinterpret_cast<const unsigned short*>(r + kValueBytes + 2 * p));
-        rsv[u][s] = src.rs[s] ? __ldg(src.rs[s] + row) : src.gs[s];
+        rsv[u][s] = src.rs[s0 + s] ? __ldg(src.rs[s0 + s] + row) : src.gs[s0 + s];
       }
-    }
+    };
+#pragma unroll
+    for (int u = 0; u < U; u++) load_batch(u, row0 + u < rows ? row0 + u : rows - 1, 0);   // clamped: extra loads are discarded
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int row = row0 + u;
@@ -189,16 +205,21 @@ decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
       float acc[32];
       zero32(acc);
 #pragma unroll
-      for (int s = 0; s < NS; s++) decode_acc_natural(acc, q[u][s], sf[u][s], rsv[u][s]);
+      for (int s0 = 0; s0 < NS; s0 += CH) {
+        if (s0) load_batch(u, row, s0);
+#pragma unroll
+        for (int s = 0; s < CH; s++) decode_acc_natural(acc, q[u][s], sf[u][s], rsv[u][s]);
+      }
       if (REENC) {
         float g6[kTeamWarps];
-        team_exchange6(xchg, phase, warp, lane, warp_max(absmax32(acc, 0.0f)), g6);
+        const float bm0 = absmax16(acc), bm1 = absmax16(acc + 16);
+        team_exchange6(xchg, phase, warp, lane, warp_max(fmaxf(bm0, bm1)), g6);
         float am = g6[0];
 #pragma unroll
         for (int g = 1; g < kTeamWarps; g++) am = fmaxf(am, g6[g]);
         const RowScale sc2 = row_scale_from_amax(am);
         uint4 qq;
-        const uint32_t sf2 = encode_pair_f32<true>(acc, [&](float b0, float b1, float& m0, float& m1) {
+        const uint32_t sf2 = encode_pair_f32<true>(acc, bm0, bm1, [&](float b0, float b1, float& m0, float& m1) {
           return pair_block_scales(b0, b1, sc2.inv, m0, m1);
         }, qq);
         char* r = rec_out + (size_t)row * kRecStride;
@@ -347,7 +368,7 @@ static int launch_decode(int nsrc, const void* const* src, long pitch, const flo
     if (!sl.rs[s]) { if (!gs) return FP4AR_ERR_ARGUMENT; sl.gs[s] = gs[s]; }
   }
   if (rows == 0) return FP4AR_OK;
-  const int grid = team_grid(rows, decode_rows_per_trip(nsrc, REENC), (nsrc > 4 || REENC) ? 3 : 4);
+  const int grid = team_grid(rows, decode_rows_per_trip(nsrc, REENC), decode_blocks_per_sm(nsrc, REENC));
 #define FP4AR_DEC_CASE(N)                                                                                          \
   case N:                                                                                                          \
     decode_sum_kernel<N, REENC><<<grid, kTeamThreads, 0, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);       \

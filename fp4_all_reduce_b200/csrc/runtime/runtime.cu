@@ -333,15 +333,18 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   prm.flags = (a0.mode == FP4AR_MODE_XPORT ? kFlagXport : 0) | (a0.mode == FP4AR_MODE_COMPUTE ? kFlagLoopback : 0);
   prm.cap = c->geo.cap; prm.capo = c->geo.capo;
   prm.buf_bytes = c->geo.buf_bytes; prm.timeout_ns = c->timeout_ns;
-  // Two-shot pipeline depths: tune[3] = lag_owner | lag_finish << 4 when set; otherwise the measured best that has
-  // also passed the bitwise gate on real GPUs.  With eight ranks every row waits on seven peers, so one more step of
-  // slack at each hand-off pays at every row count (16K rows: 284 -> 228 us).  With four ranks the kernel is bound
-  // by its own codec work at large row counts and the shallow pipeline wins there; (2,4) is about 6 % faster up to
-  // 4096 rows but has only been timed, not gated, on four GPUs, so it stays an option (tune[3] = 0x42).
+  // Two-shot pipeline depths: tune[3] = lag_owner | lag_finish << 4 when set, otherwise by team width and degree.
+  // A step of a three-warp team takes about twice as long as a step of a six-warp team, so in steps the six-warp
+  // shapes get twice the slack: (2,4) = two steps from a row's encode to its owner step and two more to its finish.
+  // Three-warp teams (measured on 4 and 8 GPUs): (1,2) at four ranks, where the kernel is bound by its own codec work
+  // at large row counts and the shallow pipeline wins; (2,3) at eight, where every row waits on seven peers and one
+  // more step of slack at each hand-off pays at every row count (16K rows: 284 -> 228 us).  Six-warp teams on emulated
+  // rank groups (4 ranks x 4096 rows on one GPU): (1,2) 191 us, (2,3) 142, (2,4) 139, (3,4) 141.
   {
     int lo = a0.tune[3] & 15, lf = (a0.tune[3] >> 4) & 15;
     if (lo < 1 || lf <= lo || lf > 4) {
-      if (c->nranks >= 6) { lo = 2; lf = 3; }
+      if (ke->T == 6) { lo = 2; lf = 4; }
+      else if (c->nranks >= 6) { lo = 2; lf = 3; }
       else { lo = 1; lf = 2; }
     }
     prm.lag_owner = lo; prm.lag_finish = lf;

@@ -1,7 +1,7 @@
 """Measurement campaign driver: runs a file of cells one after another, each as its own process tree with a
 time limit, with per-GPU locks, a wall-clock deadline, resume, and a clock guard.
 
-    python -m fp4_all_reduce_b200.harness.campaign cells.txt --out runs/ [--deadline HH:MM] [--resume]
+    python -m fp4_all_reduce_b200.harness.campaign cells.txt --out runs/ [--deadline HH:MM | +SECONDS] [--resume]
         [--expect-mem-mhz 3996] [--dry-run] [--lock-dir /tmp/fp4ar_locks] [--port 29700]
 
 Cell file, one cell per line ('#' and blank lines ignored):
@@ -257,6 +257,8 @@ def read_mem_clocks(gpus: list[int]) -> Optional[list[int]]:
 def parse_deadline(s: Optional[str], now: float) -> float:
     if not s:
         return 0.0
+    if s.startswith("+"):               # seconds from now
+        return now + float(s[1:])
     if ":" in s:
         hh, mm = s.split(":")
         lt = time.localtime(now)
@@ -350,7 +352,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("cells")
     ap.add_argument("--out", required=True)
-    ap.add_argument("--deadline", default=None, help="HH:MM (local, today) or an epoch in seconds")
+    ap.add_argument("--deadline", default=None, help="HH:MM (local, today), +SECONDS from now, or an epoch in seconds")
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--dry-run", action="store_true")
     ap.add_argument("--expect-mem-mhz", type=int, default=0)

@@ -117,7 +117,7 @@ def test_dry_run_and_deadline_parse(tmp_path, capsys):
     assert C.main([str(f), "--out", str(tmp_path / "o"), "--dry-run"]) == 0
     outp = capsys.readouterr().out
     assert "torch.distributed.run" in outp and "gate_dist" in outp
-    assert C.parse_deadline(None, 0.0) == 0.0 and C.parse_deadline("12345", 0.0) == 12345.0
+    assert C.parse_deadline(None, 0.0) == 0.0 and C.parse_deadline("12345", 0.0) == 12345.0 and C.parse_deadline("+90", 1000.0) == 1090.0
     assert C.parse_deadline("23:59", 1_700_000_000.0) > 0
 
 
