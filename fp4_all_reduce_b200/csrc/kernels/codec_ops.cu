@@ -153,28 +153,18 @@ struct SrcList {
   float gs[kMaxRanksOps];
 };
 
-#ifndef EXP_REENC_U
-#define EXP_REENC_U 2
-#endif
-#ifndef EXP_REENC_BLK
-#define EXP_REENC_BLK 3
-#endif
-#ifndef EXP_DEC8_BLK
-#define EXP_DEC8_BLK 3
-#endif
-#ifndef EXP_DEC8_CH
-#define EXP_DEC8_CH 8
-#endif
 // Rows whose loads a team issues together before the first use (bytes in flight against registers).
 __host__ __device__ constexpr int decode_rows_per_trip(int ns, bool reenc) {
-  return ns == 1 ? 4 : (ns == 2 ? 2 : (reenc && ns <= 4 ? EXP_REENC_U : 1));
+  return reenc ? 1 : (ns == 1 ? 4 : (ns == 2 ? 2 : 1));
 }
-__host__ __device__ constexpr int decode_blocks_per_sm(int ns, bool reenc) {
-  return reenc ? EXP_REENC_BLK : (ns > 4 ? EXP_DEC8_BLK : 4);
-}
+// Four teams per SM (24 warps, at most 80 registers) for every shape: these kernels are bound by instruction issue
+// (about three instructions per decoded value), so warps to choose from count for more than loads in flight per
+// thread.  Measured at 16384 rows: eight sources 143 us at three teams / 90 registers, 122 us at four / 78; the
+// owner step 128 us at three teams with two rows per trip, 122 us at four with one.
+constexpr int kDecodeTeamsPerSm = 4;
 
 template <int NS, bool REENC>
-__global__ void __launch_bounds__(kTeamThreads, decode_blocks_per_sm(NS, REENC))
+__global__ void __launch_bounds__(kTeamThreads, kDecodeTeamsPerSm)
 decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
   __shared__ __align__(128) uint8_t stage_all[kTeamWarps * kStageBytes];
   __shared__ float xchg[16];
@@ -183,21 +173,20 @@ decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
   int phase = 0;
   constexpr int U = decode_rows_per_trip(NS, REENC);
   for (int row0 = blockIdx.x * U; row0 < rows; row0 += gridDim.x * U) {
-    constexpr int CH = (NS > 4 && U == 1) ? EXP_DEC8_CH : NS;     // sources loaded together
-    uint4 q[U][CH];
-    uint32_t sf[U][CH];
-    float rsv[U][CH];
-    auto load_batch = [&](int u, int row, int s0) {
+    uint4 q[U][NS];
+    uint32_t sf[U][NS];
+    float rsv[U][NS];
 #pragma unroll
-      for (int s = 0; s < CH; s++) {
-        const char* r = src.base[s0 + s] + (size_t)row * pitch;
+    for (int u = 0; u < U; u++) {
+      const int row = row0 + u < rows ? row0 + u : rows - 1;     // clamped: the extra loads are discarded
+#pragma unroll
+      for (int s = 0; s < NS; s++) {
+        const char* r = src.base[s] + (size_t)row * pitch;
         q[u][s] = __ldcs(reinterpret_cast<const uint4*>(r + 16 * p));
         sf[u][s] = __ldcs(reinterpret_cast<const unsigned short*>(r + kValueBytes + 2 * p));
-        rsv[u][s] = src.rs[s0 + s] ? __ldg(src.rs[s0 + s] + row) : src.gs[s0 + s];
+        rsv[u][s] = src.rs[s] ? __ldg(src.rs[s] + row) : src.gs[s];
       }
-    };
-#pragma unroll
-    for (int u = 0; u < U; u++) load_batch(u, row0 + u < rows ? row0 + u : rows - 1, 0);   // clamped: extra loads are discarded
+    }
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int row = row0 + u;
@@ -205,11 +194,7 @@ decode_sum_kernel(SrcList src, long pitch, int rows, char* rec_out, char* out) {
       float acc[32];
       zero32(acc);
 #pragma unroll
-      for (int s0 = 0; s0 < NS; s0 += CH) {
-        if (s0) load_batch(u, row, s0);
-#pragma unroll
-        for (int s = 0; s < CH; s++) decode_acc_natural(acc, q[u][s], sf[u][s], rsv[u][s]);
-      }
+      for (int s = 0; s < NS; s++) decode_acc_natural(acc, q[u][s], sf[u][s], rsv[u][s]);
       if (REENC) {
         float g6[kTeamWarps];
         const float bm0 = absmax16(acc), bm1 = absmax16(acc + 16);
@@ -368,7 +353,7 @@ static int launch_decode(int nsrc, const void* const* src, long pitch, const flo
     if (!sl.rs[s]) { if (!gs) return FP4AR_ERR_ARGUMENT; sl.gs[s] = gs[s]; }
   }
   if (rows == 0) return FP4AR_OK;
-  const int grid = team_grid(rows, decode_rows_per_trip(nsrc, REENC), decode_blocks_per_sm(nsrc, REENC));
+  const int grid = team_grid(rows, decode_rows_per_trip(nsrc, REENC), kDecodeTeamsPerSm);
 #define FP4AR_DEC_CASE(N)                                                                                          \
   case N:                                                                                                          \
     decode_sum_kernel<N, REENC><<<grid, kTeamThreads, 0, st>>>(sl, pitch, rows, (char*)rec_out, (char*)out);       \
