@@ -65,7 +65,7 @@ typedef struct fp4ar_args {
   int tune[4];            /* [0] teams per CTA (0 = default), [1] bit 0: no programmatic dependent launch,
                              [2] warps per row team (0 = default: 6 for two-shot at 4 and 8 ranks, else 3; compiled widths:
                              3 for every shape, 6 for the two-shot shapes of 4 and 8 ranks),
-                             [3] two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default: (2,4) with six-warp teams,
+                             [3] two-shot pipeline depths, lag_owner | lag_finish << 4 (0 = default: (2,3) with six-warp teams,
                                  (1,2) / (2,3) with three-warp teams at up to four / more ranks) */
 } fp4ar_args;
 

@@ -8,8 +8,10 @@
 //                 where the AllReduce kernel in "pushed input" mode finds them, and/or
 //               - into a local [M, N/2 + N/16] NVFP4 tensor.
 //
-// sm_100a structure: persistent CTAs (one per SM), 128 x 256 or 128 x 192 output tiles (whichever fills the last wave
-// of the 148 CTAs better), K in blocks of 64.
+// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.  Where the tile count is
+// not a multiple of the CTA count, the first (CTAs + remainder) tiles are cut along K into equal ranges per CTA
+// (stream-K, see SegIter) so that no CTA idles through a last wave; 128 x 192 tiles are the fallback where that does
+// not apply (fewer tiles than CTAs).
 //   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
 //                              128-byte swizzle, completion on mbarriers
 //   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
@@ -73,6 +75,10 @@ struct GemmParams {
   float* dbg_acc;      // [M][N]
   StatusWords* status;
   unsigned long long timeout_ns;
+  // split of the K loop across CTAs (see SegIter): partial accumulators and their flags, one slot per CTA
+  int stream_k;
+  float* sk_partial;     // [grid][BN / 32][8][128] float4
+  uint32_t* sk_flags;    // [grid][4]: 1 = the slot's quarter (32 rows) is written and not yet consumed
 };
 
 // ---- tcgen05 / TMA wrappers ----
@@ -166,6 +172,84 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, const 
   return true;
 }
 
+// Bounded wait until *flag == want (acquire); false when it gave up or the CTA is aborting.
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool gemm_flag_wait(const uint32_t* flag, uint32_t want, const GemmWait& w, uint32_t what) {
+  if (ld_acquire_gpu(flag) == want) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t n = 0;
+  while (ld_acquire_gpu(flag) != want) {
+    if ((++n & 63u) == 0u) {
+      if (*w.abort_flag) return false;
+      if (global_timer_ns() - t0 > w.limit_ns) {
+        *w.abort_flag = 1u;
+        if (atomicCAS(&w.status->code, 0u, (uint32_t)kStatusLoadTimeout) == 0u) { w.status->detail = 16u + what; w.status->cta = blockIdx.x; }
+        atomicAdd(&w.status->count, 1u);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// The work of one CTA as a list of segments (tile, K blocks [lo, lo + count), rotation), the same list in all three roles.
+//   plain:    whole tiles blockIdx.x, blockIdx.x + grid, ...
+//   stream-K: with tiles = w * grid + r (0 < r < grid) the first grid + r tiles are cut, as tiles x kblocks units,
+//             into `grid` equal contiguous ranges, so every CTA runs the same number of K blocks there (between one and
+//             two tiles' worth) instead of r CTAs running one more tile than the others; the other (w - 1) * grid
+//             tiles follow as whole tiles.  A range is at least one tile long, so a tile is shared by at most two
+//             CTAs: the one whose range BEGINS inside the tile (kProduce) runs its share first, on the tile's FIRST K
+//             blocks, and leaves its FP32 accumulator in its slot of the partial buffer; the one whose range ENDS
+//             inside the tile (kFix) runs the remaining K blocks last, adds that partial and does the tile's epilogue.
+//             The partial was written about one tile duration or more before it is read.
+//   rotation: a segment walks its K blocks cyclically, starting where the CTA's running count of K blocks (the same
+//             clock in every CTA) points, so that at any moment all CTAs read the same 64-column slice of X and Wt
+//             whatever tile they are on: the operands stay L2 resident although the ranges start at unrelated K
+//             offsets.  (Ranges walked from their own first block were measured 30 % slower at M = 1024, K = 8192.)
+enum : int { kWhole = 0, kProduce = 1, kFix = 2 };
+struct Seg { int tile, lo, count, first, kind; };      // K block of step j: lo + (first + j) % count
+struct SegIter {
+  int tiles, kblocks, stride, t;
+  long long u, u_end, tau;
+  __device__ SegIter(int stream_k, int tiles_, int kblocks_) : tiles(tiles_), kblocks(kblocks_), stride(gridDim.x), tau(0) {
+    const int g = gridDim.x;
+    const int cut_tiles = stream_k ? g + tiles_ % g : 0;
+    const long long total = (long long)cut_tiles * kblocks_;
+    u = total * blockIdx.x / g;
+    u_end = total * (blockIdx.x + 1) / g;
+    t = cut_tiles + blockIdx.x;
+  }
+  __device__ bool next(Seg& s) {
+    if (u < u_end) {
+      s.tile = (int)(u / kblocks);
+      const int off = (int)(u - (long long)s.tile * kblocks);
+      const long long left = u_end - u;
+      const int room = kblocks - off;
+      s.count = (int)(left < room ? left : room);
+      if (off > 0) { s.kind = kProduce; s.lo = 0; }
+      else if (s.count < kblocks) { s.kind = kFix; s.lo = kblocks - s.count; }
+      else { s.kind = kWhole; s.lo = 0; }
+      u += s.count;
+    } else {
+      if (t >= tiles) return false;
+      s.tile = t; s.lo = 0; s.count = kblocks; s.kind = kWhole;
+      t += stride;
+    }
+    const int phase = (int)(tau % kblocks) - s.lo;
+    s.first = phase >= 0 && phase < s.count ? phase : 0;
+    tau += s.count;
+    return true;
+  }
+  __device__ static int kblock(const Seg& s, int j) { const int r = s.first + j; return s.lo + (r >= s.count ? r - s.count : r); }
+};
+
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -208,10 +292,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
-      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+      SegIter seg(p.stream_k, tiles, kblocks);
+      Seg sg;
+      while (seg.next(sg)) {
         int m0, n0;
-        tile_coords<BN>(t, m_tiles, n_tiles, m0, n0);
-        for (int kb = 0; kb < kblocks; kb++, it++) {
+        tile_coords<BN>(sg.tile, m_tiles, n_tiles, m0, n0);
+        for (int j = 0; j < sg.count; j++, it++) {
+          const int kb = SegIter::kblock(sg, j);
           const int s = it % kStages;
           if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
             // giving up: let the loads already issued land before the CTA (and its shared memory) goes away
@@ -232,12 +319,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t it = 0, tile_i = 0;
-      for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
+      SegIter seg(p.stream_k, tiles, kblocks);
+      Seg sg;
+      for (; seg.next(sg); tile_i++) {
         const uint32_t a = tile_i & 1u;
         if (!gemm_wait(acc_empty + a, ((tile_i >> 1) & 1u) ^ 1u, gw, 2)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
-        for (int kb = 0; kb < kblocks; kb++, it++) {
+        for (int j = 0; j < sg.count; j++, it++) {
           const int s = it % kStages;
           if (!gemm_wait(full + s, (it / kStages) & 1u, gw, 3)) goto done;
           tc_fence_after();
@@ -245,7 +334,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const uint64_t db = umma_desc_k128(ring + s * kStageBytes + kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / 16; k++)
-            umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (j | k) != 0 ? 1u : 0u);
           umma_commit(empty + s);          // the stage is free once these MMAs have read it
         }
         umma_commit(acc_full + a);         // the accumulator is complete once everything above has run
@@ -259,17 +348,63 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const size_t buf_off = p.nranks ? (size_t)(*p.call_counter & 1u) * p.buf_bytes : 0;
     const int qrow_bytes = p.N / 2 + p.N / 16;
     uint32_t tile_i = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, tile_i++) {
+    SegIter seg(p.stream_k, tiles, kblocks);
+    Seg sg;
+    // this thread's float4 i of chunk c inside a partial slot: a warp's 32 rows are 512 contiguous bytes
+    auto slot_ptr = [&](int cta, int c, int i) {
+      return reinterpret_cast<float4*>(p.sk_partial) + ((size_t)cta * (BN / 32) + c) * 8 * kBM + (size_t)i * kBM + r_in_tile;
+    };
+    for (; seg.next(sg); tile_i++) {
       int m0, n0;
-      tile_coords<BN>(t, m_tiles, n_tiles, m0, n0);
+      tile_coords<BN>(sg.tile, m_tiles, n_tiles, m0, n0);
       const uint32_t a = tile_i & 1u;
       const int row = m0 + r_in_tile;
+      const bool produces = sg.kind == kProduce;           // a share of the tile's K blocks: leave a partial
+      const bool fixes = sg.kind == kFix;                  // the rest of them: add the next CTA's partial
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
+      if (produces) {
+        // the slot is free once the consumer of an earlier launch has reset the flag
+        uint32_t* flag = p.sk_flags + blockIdx.x * 4 + q;
+        bool ok = lane == 0 ? gemm_flag_wait(flag, 0u, gw, 5) : true;
+        ok = __all_sync(0xffffffffu, ok) && __all_sync(0xffffffffu, gemm_wait(acc_full + a, (tile_i >> 1) & 1u, gw, 4));
+        if (!ok) break;
+        tc_fence_after();
+        float v[2][32];
+        tmem_ld32_issue(tbase, v[0]);
+#pragma unroll
+        for (int c = 0; c < BN / 32; c++) {
+          tmem_ld_wait();
+          if (c + 1 < BN / 32) tmem_ld32_issue(tbase + (c + 1) * 32, v[(c + 1) & 1]);
+          const float* vc = v[c & 1];
+#pragma unroll
+          for (int i = 0; i < 8; i++) *slot_ptr(blockIdx.x, c, i) = make_float4(vc[4 * i], vc[4 * i + 1], vc[4 * i + 2], vc[4 * i + 3]);
+        }
+        tc_fence_before();
+        mbar_arrive(acc_empty + a);
+        __syncwarp();
+        if (lane == 0) { __threadfence(); st_release_gpu(flag, 1u); }
+        continue;
+      }
+      float pv[2][32];
+      uint32_t* fix_flag = p.sk_flags + (blockIdx.x + 1) * 4 + q;
+      auto load_partial = [&](int c, float* dst) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float4 f = __ldcg(slot_ptr(blockIdx.x + 1, c, i));
+          dst[4 * i] = f.x; dst[4 * i + 1] = f.y; dst[4 * i + 2] = f.z; dst[4 * i + 3] = f.w;
+        }
+      };
+      if (fixes) {
+        // written about one kernel duration ago; fetched while the last K blocks of this tile are still running
+        bool ok = lane == 0 ? gemm_flag_wait(fix_flag, 1u, gw, 6) : true;
+        if (!__all_sync(0xffffffffu, ok)) break;
+        load_partial(0, pv[0]);
+      }
       // warp-uniform verdict: the tcgen05.ld below is a warp-wide instruction
       if (!__all_sync(0xffffffffu, gemm_wait(acc_full + a, (tile_i >> 1) & 1u, gw, 4))) break;
       tc_fence_after();
       bulk_wait_source_free<0>();   // this thread's previous pieces have left its staging row
       // 32 columns at a time, double-buffered: the load of chunk c + 1 is in flight while chunk c is quantised
-      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
       float v[2][32];
       tmem_ld32_issue(tbase, v[0]);
 #pragma unroll
@@ -277,6 +412,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         tmem_ld_wait();
         if (c + 1 < BN / 32) tmem_ld32_issue(tbase + (c + 1) * 32, v[(c + 1) & 1]);
         float* vc = v[c & 1];
+        if (fixes) {
+          if (c + 1 < BN / 32) load_partial(c + 1, pv[(c + 1) & 1]);
+          const float* pc = pv[c & 1];
+#pragma unroll
+          for (int i = 0; i < 32; i++) vc[i] = __fadd_rn(vc[i], pc[i]);
+        }
         if (p.dbg_acc && row < p.M) {
           float4* dst = reinterpret_cast<float4*>(p.dbg_acc + (size_t)row * p.N + n0 + c * 32);
 #pragma unroll
@@ -288,6 +429,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }, qv);
         *reinterpret_cast<uint4*>(my_piece + 16 * c) = qv;
         *reinterpret_cast<uint16_t*>(my_piece + S::kValueB + 2 * c) = (uint16_t)sf2;
+      }
+      if (fixes) {
+        __syncwarp();
+        if (lane == 0) st_release_gpu(fix_flag, 0u);        // every lane has its partial in registers: the slot is free
       }
       tc_fence_before();
       mbar_arrive(acc_empty + a);                 // 128 arrivals hand the accumulator back to the MMA warp
@@ -365,6 +510,30 @@ static StatusWords* gemm_status_word() {
   return p[dev];
 }
 
+// Partial accumulators of the stream-K split: one slot of 128 x 256 floats and four flags per SM, allocated at the
+// first call on a device and kept (19 MB on a B200).  Launches that share a device take turns on a slot through its
+// flags: a producer waits until the consumer of the previous launch has reset them.
+struct StreamKSpace { float* partial; uint32_t* flags; int slots; };
+static bool stream_k_space(int slots, StreamKSpace* out) {
+  static StreamKSpace sp[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (!sp[dev].partial) {
+    float* part = nullptr;
+    uint32_t* fl = nullptr;
+    const size_t pbytes = (size_t)slots * kBM * 256 * sizeof(float), fbytes = (size_t)slots * 4 * sizeof(uint32_t);
+    if (cudaMalloc(&part, pbytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMalloc(&fl, fbytes) != cudaSuccess) { cudaGetLastError(); cudaFree(part); return false; }
+    if (cudaMemset(fl, 0, fbytes) != cudaSuccess) { cudaGetLastError(); cudaFree(part); cudaFree(fl); return false; }
+    sp[dev] = StreamKSpace{part, fl, slots};
+  }
+  if (sp[dev].slots < slots) return false;
+  *out = sp[dev];
+  return true;
+}
+
 }  // namespace fp4ar
 
 using namespace fp4ar;
@@ -376,6 +545,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   const int tiles = (p.N / BN) * ((p.M + kBM - 1) / kBM);
   const int sms = device_sm_count();
   const int grid = tiles < sms ? tiles : sms;
+  if (p.stream_k && grid != sms) return FP4AR_ERR_ARGUMENT;      // the split needs tiles >= CTAs, one CTA per SM
   gemm_nvfp4_kernel<BN><<<grid, kGemmThreads, S::kSmem, stream>>>(ma, mb, p);
   return cuda_check_launch();
 }
@@ -389,6 +559,7 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   // about 0.87 of the per-cycle work of a 256-wide one (M = 4096: 321 vs 315 us at K = 8192 although its last wave
   // is full), so it is only taken where it wins clearly (M = 1024: 111 vs 123 us); N must be a multiple of 192 too.
   int bn = 256;
+  bool stream_k = false;
   {
     const char* force = std::getenv("FP4AR_GEMM_TILE_N");
     const int sms = device_sm_count();
@@ -399,6 +570,13 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
     if (N % 192 == 0 && 0.80 * busy(192) > busy(256)) bn = 192;
     if (force && std::atoi(force) == 256) bn = 256;
     if (force && std::atoi(force) == 192 && N % 192 == 0) bn = 192;
+    // Stream-K (256-wide tiles, the K loop cut into equal ranges per CTA) where whole tiles would leave the last wave
+    // of CTAs partly idle; FP4AR_GEMM_STREAM_K = 0 / 1 overrides.
+    const long tiles256 = (long)(N / 256) * ((M + kBM - 1) / kBM);
+    stream_k = tiles256 > sms && tiles256 % sms != 0 && busy(256) < 0.95 && !(force && std::atoi(force) == 192);
+    const char* fsk = std::getenv("FP4AR_GEMM_STREAM_K");
+    if (fsk) stream_k = std::atoi(fsk) != 0 && tiles256 > sms && tiles256 % sms != 0;
+    if (stream_k) bn = 256;
   }
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -421,6 +599,10 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   p.status = gemm_status_word();
   if (!p.status) return cuda_fail();
   p.timeout_ns = 2000000000ull;
+  if (stream_k) {
+    StreamKSpace sp;
+    if (stream_k_space(device_sm_count(), &sp)) { p.stream_k = 1; p.sk_partial = sp.partial; p.sk_flags = sp.flags; }
+  }
   CUtensorMap ma, mb;
   if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, bn)) return FP4AR_ERR_UNSUPPORTED;
   return bn == 192 ? launch_gemm<192>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256>(ma, mb, p, (cudaStream_t)stream);

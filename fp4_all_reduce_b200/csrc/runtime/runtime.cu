@@ -334,17 +334,16 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   prm.cap = c->geo.cap; prm.capo = c->geo.capo;
   prm.buf_bytes = c->geo.buf_bytes; prm.timeout_ns = c->timeout_ns;
   // Two-shot pipeline depths: tune[3] = lag_owner | lag_finish << 4 when set, otherwise by team width and degree.
-  // A step of a three-warp team takes about twice as long as a step of a six-warp team, so in steps the six-warp
-  // shapes get twice the slack: (2,4) = two steps from a row's encode to its owner step and two more to its finish.
   // Three-warp teams (measured on 4 and 8 GPUs): (1,2) at four ranks, where the kernel is bound by its own codec work
   // at large row counts and the shallow pipeline wins; (2,3) at eight, where every row waits on seven peers and one
-  // more step of slack at each hand-off pays at every row count (16K rows: 284 -> 228 us).  Six-warp teams on emulated
-  // rank groups (4 ranks x 4096 rows on one GPU): (1,2) 191 us, (2,3) 142, (2,4) 139, (3,4) 141.
+  // more step of slack at each hand-off pays at every row count (16K rows: 284 -> 228 us).  A step of a six-warp team
+  // takes about half as long, so those shapes run (2,3) everywhere.  Eight GPUs, 16384 rows, AR / block: (2,3) 179 /
+  // 238 us, (2,4) 192 / 240, (3,4) 181 / 240; 1024 rows: 24.6, 27.6, 23.2 us.  Four emulated ranks x 4096 rows on one
+  // GPU: (1,2) 191 us, (2,3) 142, (2,4) 139, (3,4) 141.
   {
     int lo = a0.tune[3] & 15, lf = (a0.tune[3] >> 4) & 15;
     if (lo < 1 || lf <= lo || lf > 4) {
-      if (ke->T == 6) { lo = 2; lf = 4; }
-      else if (c->nranks >= 6) { lo = 2; lf = 3; }
+      if (ke->T == 6 || c->nranks >= 6) { lo = 2; lf = 3; }
       else { lo = 1; lf = 2; }
     }
     prm.lag_owner = lo; prm.lag_finish = lf;

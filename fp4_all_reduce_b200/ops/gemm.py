@@ -40,10 +40,15 @@ def calibrate_gs(x: torch.Tensor, wt: torch.Tensor) -> float:
     return max(float(y.abs().max().item()), 1e-30) / 2688.0
 
 
-def gemm_nvfp4(x: torch.Tensor, wt: torch.Tensor, gs: float, *, want_acc: bool = False):
-    """Local NVFP4 rows of x @ wt.T; with want_acc also the kernel's FP32 accumulators [M, N]."""
+def gemm_nvfp4(x: torch.Tensor, wt: torch.Tensor, gs: float, *, want_acc: bool = False, out: Optional[torch.Tensor] = None):
+    """Local NVFP4 rows of x @ wt.T (into `out` when given); with want_acc also the kernel's FP32 accumulators [M, N]."""
     M, Nn, K = _check(x, wt)
-    q = torch.empty(M, Nn // 2 + Nn // 16, dtype=torch.uint8, device=x.device)
+    if out is None:
+        q = torch.empty(M, Nn // 2 + Nn // 16, dtype=torch.uint8, device=x.device)
+    else:
+        q = out
+        if q.dtype != torch.uint8 or tuple(q.shape) != (M, Nn // 2 + Nn // 16) or not q.is_contiguous() or q.device != x.device:
+            raise ValueError("out must be a contiguous uint8 [M, N/2 + N/16] tensor on the device of x")
     acc = torch.empty(M, Nn, dtype=torch.float32, device=x.device) if want_acc else None
     with torch.cuda.device(x.device):
         N.check(N.cuda().fp4ar_gemm_nvfp4(None, 0, x.data_ptr(), wt.data_ptr(), M, Nn, K, C.c_float(gs), q.data_ptr(),

@@ -67,3 +67,47 @@ def test_gemm_push_then_allreduce_on_emulated_ranks(P):
             assert np.array_equal(O.bf16_bits(outs[r]), exp["out"]), (call, r)
             assert np.array_equal(O.bf16_bits(res[r]), exp["res_out"]), (call, r)
     g.close()
+
+
+@pytest.mark.parametrize("M,K", [(1024, 2048), (2048, 512), (1000, 1024), (2300, 320)])
+def test_gemm_stream_k_split(M, K, monkeypatch):
+    """Tile counts that do not fill the last wave of CTAs run with the K loop cut into equal ranges per CTA: a tile shared
+    by two CTAs is summed from a partial accumulator.  Same checks as for whole tiles, over several calls (the partial
+    slots and their flags are reused), inside a CUDA graph of back-to-back launches, and against the whole-tile walk."""
+    Nn = N.HIDDEN
+    x, wt = _xw(M, K, Nn, 3)
+    gs = G.calibrate_gs(x, wt)
+    ref = x.float() @ wt.float().t()
+    tol = 2e-3 * ref.abs().max().item() + 1e-4
+    monkeypatch.setenv("FP4AR_GEMM_STREAM_K", "0")
+    q_plain, acc_plain = G.gemm_nvfp4(x, wt, gs, want_acc=True)
+    torch.cuda.synchronize()
+    monkeypatch.setenv("FP4AR_GEMM_STREAM_K", "1")
+    for call in range(3):
+        q, acc = G.gemm_nvfp4(x, wt, gs, want_acc=True)
+        torch.cuda.synchronize()
+        assert G.gemm_status().code == 0
+        assert (acc - ref).abs().max().item() <= tol
+        want = O.encode_static_f32(acc.cpu().numpy(), gs)
+        assert np.count_nonzero(q.cpu().numpy() != want) == 0
+        # the split changes the order of the FP32 additions, nothing else
+        assert (acc - acc_plain).abs().max().item() <= 1e-5 * ref.abs().max().item() + 1e-6
+    assert (q != q_plain).float().mean().item() < 0.01
+    first = q.clone()
+    st = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    outs = [torch.empty_like(q) for _ in range(3)]
+    with torch.cuda.stream(st):
+        G.gemm_nvfp4(x, wt, gs, out=outs[0])
+        st.synchronize()
+        with torch.cuda.graph(g, stream=st):
+            for o in outs:
+                G.gemm_nvfp4(x, wt, gs, out=o)
+    for _ in range(2):
+        for o in outs:
+            o.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert G.gemm_status().code == 0
+        for o in outs:
+            assert torch.equal(o, first)
