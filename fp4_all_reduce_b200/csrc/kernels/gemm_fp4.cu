@@ -209,16 +209,19 @@ __device__ __forceinline__ bool gemm_flag_wait(const uint32_t* flag, uint32_t wa
 //             blocks, and leaves its FP32 accumulator in its slot of the partial buffer; the one whose range ENDS
 //             inside the tile (kFix) runs the remaining K blocks last, adds that partial and does the tile's epilogue.
 //             The partial was written about one tile duration or more before it is read.
-//   rotation: a segment walks its K blocks cyclically, starting where the CTA's running count of K blocks (the same
-//             clock in every CTA) points, so that at any moment all CTAs read the same 64-column slice of X and Wt
-//             whatever tile they are on: the operands stay L2 resident although the ranges start at unrelated K
-//             offsets.  (Ranges walked from their own first block were measured 30 % slower at M = 1024, K = 8192.)
+//   K order:  every segment walks its K blocks upwards.  The producing share is the tile's FIRST K blocks and the fixing
+//             share its LAST ones, so a CTA that starts with a share of c blocks is at block t while it produces, at
+//             t - c in the whole tile that follows and at most (range - kblocks) behind t in its fixing share: at
+//             any moment all CTAs read 64-column slices of X and Wt that lie within that window of each other and no
+//             slice is needed again after the window has passed, so the operands cross HBM once.  (Shares that start
+//             at unrelated K offsets: 123 us at M = 1024, K = 8192; a cyclic walk locked to a common clock: 94 us,
+//             267 MB of DRAM reads for 116 MB of operands because the wrapped part is re-read.)
 enum : int { kWhole = 0, kProduce = 1, kFix = 2 };
-struct Seg { int tile, lo, count, first, kind; };      // K block of step j: lo + (first + j) % count
+struct Seg { int tile, lo, count, kind; };      // K blocks lo .. lo + count - 1
 struct SegIter {
   int tiles, kblocks, stride, t;
-  long long u, u_end, tau;
-  __device__ SegIter(int stream_k, int tiles_, int kblocks_) : tiles(tiles_), kblocks(kblocks_), stride(gridDim.x), tau(0) {
+  long long u, u_end;
+  __device__ SegIter(int stream_k, int tiles_, int kblocks_) : tiles(tiles_), kblocks(kblocks_), stride(gridDim.x) {
     const int g = gridDim.x;
     const int cut_tiles = stream_k ? g + tiles_ % g : 0;
     const long long total = (long long)cut_tiles * kblocks_;
@@ -242,12 +245,8 @@ struct SegIter {
       s.tile = t; s.lo = 0; s.count = kblocks; s.kind = kWhole;
       t += stride;
     }
-    const int phase = (int)(tau % kblocks) - s.lo;
-    s.first = phase >= 0 && phase < s.count ? phase : 0;
-    tau += s.count;
     return true;
   }
-  __device__ static int kblock(const Seg& s, int j) { const int r = s.first + j; return s.lo + (r >= s.count ? r - s.count : r); }
 };
 
 template <int BN>
@@ -298,7 +297,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         int m0, n0;
         tile_coords<BN>(sg.tile, m_tiles, n_tiles, m0, n0);
         for (int j = 0; j < sg.count; j++, it++) {
-          const int kb = SegIter::kblock(sg, j);
+          const int kb = sg.lo + j;
           const int s = it % kStages;
           if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
             // giving up: let the loads already issued land before the CTA (and its shared memory) goes away
@@ -571,9 +570,12 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
     if (force && std::atoi(force) == 256) bn = 256;
     if (force && std::atoi(force) == 192 && N % 192 == 0) bn = 192;
     // Stream-K (256-wide tiles, the K loop cut into equal ranges per CTA) where whole tiles would leave the last wave
-    // of CTAs partly idle; FP4AR_GEMM_STREAM_K = 0 / 1 overrides.
+    // of CTAs partly idle and the K loop is long enough to pay for the partial sums (K = 2048: 36.9 us against 33.0 us
+    // with whole 192-wide tiles at M = 1024, level at M = 2048, 77.8 against 79.9 at M = 4096; K = 8192: 86 / 143 /
+    // 264 us against 96 / 154 / 296 at M = 1024 / 2048 / 4096); FP4AR_GEMM_STREAM_K = 0 / 1 overrides.
     const long tiles256 = (long)(N / 256) * ((M + kBM - 1) / kBM);
-    stream_k = tiles256 > sms && tiles256 % sms != 0 && busy(256) < 0.95 && !(force && std::atoi(force) == 192);
+    stream_k = tiles256 > sms && tiles256 % sms != 0 && busy(256) < 0.95 && (K >= 4096 || tiles256 >= 4 * sms) &&
+               !(force && std::atoi(force) == 192);
     const char* fsk = std::getenv("FP4AR_GEMM_STREAM_K");
     if (fsk) stream_k = std::atoi(fsk) != 0 && tiles256 > sms && tiles256 % sms != 0;
     if (stream_k) bn = 256;
