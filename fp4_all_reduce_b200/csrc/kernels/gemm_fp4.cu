@@ -48,18 +48,24 @@ constexpr int kMaxStages = 6;
 // how full the last wave is: M = 1024, N = 6144 gives 192 tiles of 128 x 256 (1.3 waves, 65 % busy) but 256 tiles of
 // 128 x 192 (1.7 waves, 86 % busy).  (A 128-wide tile with a 6-stage ring was measured 15-35 % slower at every M from
 // 1024 to 4096 and is not built.)
-template <int BN>
+// G = 2: two CTAs of a cluster (an SM pair) work on one 256 x 256 tile with tcgen05 cta_group::2: each CTA loads its own
+// 128 rows of A and HALF of the B block (128 of the 256 columns), the tensor cores of both SMs read both halves, and
+// each CTA's TMEM holds the accumulator of its own 128 rows.  A K block then costs a CTA 32 KB of shared-memory fill
+// instead of 48 KB, and the ring is six stages deep.
+template <int BN, int G = 1>
 struct GemmShape {
   static_assert(BN == 256 || BN == 192, "tile width");
-  static constexpr int kStages = BN == 256 ? 4 : 5;
-  static constexpr int kBBytes = BN * kBK * 2;                  // 32 KB / 24 KB
-  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 40 KB
+  static_assert(G == 1 || (G == 2 && BN == 256), "CTA pairs use the 256-wide tile");
+  static constexpr int kStages = G == 2 ? 6 : (BN == 256 ? 4 : 5);
+  static constexpr int kBBytes = BN / G * kBK * 2;              // 32 KB / 24 KB, 16 KB per CTA of a pair
+  static constexpr int kStageBytes = kABytes + kBBytes;         // 48 KB / 40 KB / 32 KB
+  static constexpr int kTxBytes = kStageBytes * G;              // what lands per stage under the (leader's) full barrier
   static constexpr int kValueB = BN / 2, kScaleB = BN / 16;     // 128 + 16 B / 96 + 12 B of one row of one tile
   static constexpr int kPieceBytes = (kValueB + kScaleB + 15) & ~15;   // 144 / 112: keeps every piece 16-byte aligned
   static constexpr int kEpiBytes = kBM * kPieceBytes;
   static constexpr int kSmem = kStages * kStageBytes + kEpiBytes + 256 + 1024;   // + barriers + alignment slack
-  // Instruction descriptor: D = F32, A = B = BF16, both K-major, N = BN, M = 128.
-  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  // Instruction descriptor: D = F32, A = B = BF16, both K-major, N = BN, M = 128 per CTA of the group.
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((kBM * G) >> 4) << 24);
 };
 
 struct GemmParams {
@@ -106,6 +112,47 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// ---- CTA pair (cluster of two) ----
+__device__ __forceinline__ uint32_t cluster_cta_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_addr(local)), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load of one CTA of a pair: the bytes are counted under the barrier at `cluster_bar` (the leader's), no multicast
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(holder)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{ .reg .pred p;\n"
+               "  setp.ne.b32 p, %4, 0;\n"
+               "  tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+// arrives on the barrier at the same shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("{ .reg .b16 m;\n"
+               "  mov.b16 m, 3;\n"
+               "  tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m; }"
+               ::"r"(smem_addr(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -139,13 +186,13 @@ __device__ __forceinline__ uint64_t umma_desc_k128(const void* smem_tile) {
 // N fastest and then M.  The ~148 tiles in flight at a time then cover about 18 row blocks x 8 column tiles, which
 // needs (18 + 2*8) * 128 * K * 2 bytes of operands from L2 instead of (6 + 2*24) for a plain row-major walk.
 constexpr int kPanel = 8;
-template <int BN>
+template <int BN, int G = 1>
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m0, int& n0) {
   const int per_panel = m_tiles * kPanel;
   const int panel = t / per_panel, within = t - panel * per_panel;
   const int width = min(kPanel, n_tiles - panel * kPanel);
   const int m = within / width, n = panel * kPanel + within % width;
-  m0 = m * kBM; n0 = n * BN;
+  m0 = m * kBM * G; n0 = n * BN;
 }
 
 struct GemmWait {
@@ -221,13 +268,14 @@ struct Seg { int tile, lo, count, kind; };      // K blocks lo .. lo + count - 1
 struct SegIter {
   int tiles, kblocks, stride, t;
   long long u, u_end;
-  __device__ SegIter(int stream_k, int tiles_, int kblocks_) : tiles(tiles_), kblocks(kblocks_), stride(gridDim.x) {
-    const int g = gridDim.x;
+  // unit = this CTA (or CTA pair) among `units` of them
+  __device__ SegIter(int stream_k, int tiles_, int kblocks_, int unit, int units) : tiles(tiles_), kblocks(kblocks_), stride(units) {
+    const int g = units;
     const int cut_tiles = stream_k ? g + tiles_ % g : 0;
     const long long total = (long long)cut_tiles * kblocks_;
-    u = total * blockIdx.x / g;
-    u_end = total * (blockIdx.x + 1) / g;
-    t = cut_tiles + blockIdx.x;
+    u = total * unit / g;
+    u_end = total * (unit + 1) / g;
+    t = cut_tiles + unit;
   }
   __device__ bool next(Seg& s) {
     if (u < u_end) {
@@ -249,11 +297,11 @@ struct SegIter {
   }
 };
 
-template <int BN>
+template <int BN, int G>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ GemmParams p) {
-  using S = GemmShape<BN>;
+  using S = GemmShape<BN, G>;
   constexpr int kStages = S::kStages, kStageBytes = S::kStageBytes, kEpiBytes = S::kEpiBytes, kPieceBytes = S::kPieceBytes;
   constexpr uint32_t kIdesc = S::kIdesc;
   extern __shared__ uint8_t smem_raw[];
@@ -268,18 +316,26 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = p.N / BN, m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = p.N / BN, m_tiles = (p.M + kBM * G - 1) / (kBM * G);
   const int tiles = n_tiles * m_tiles, kblocks = p.K / kBK;
+  // a pair works as one unit: the even CTA (cluster rank 0) leads, i.e. owns the barriers the MMAs wait on and issues them
+  const uint32_t crank = G == 2 ? cluster_cta_rank() : 0u;
+  const bool leads = crank == 0u;
+  const int unit = blockIdx.x / G, units = gridDim.x / G;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 128); }
+    for (int a = 0; a < 2; a++) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 128 * G); }
     *abort_flag = 0u;
     mbar_init_fence();
   }
-  if (warp == 1) { tmem_alloc(tmem_holder, kTmemCols); tmem_relinquish(); }
+  if (warp == 1) {
+    if constexpr (G == 2) { tmem_alloc_pair(tmem_holder, kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_holder, kTmemCols); tmem_relinquish(); }
+  }
   tc_fence_before();
   __syncthreads();
+  if constexpr (G == 2) cluster_sync_all();     // the partner's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   GemmWait gw{abort_flag, p.status, p.timeout_ns};
@@ -291,34 +347,46 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
-      SegIter seg(p.stream_k, tiles, kblocks);
+      SegIter seg(p.stream_k, tiles, kblocks, unit, units);
       Seg sg;
       while (seg.next(sg)) {
         int m0, n0;
-        tile_coords<BN>(sg.tile, m_tiles, n_tiles, m0, n0);
+        tile_coords<BN, G>(sg.tile, m_tiles, n_tiles, m0, n0);
         for (int j = 0; j < sg.count; j++, it++) {
           const int kb = sg.lo + j;
           const int s = it % kStages;
           if (!gemm_wait(empty + s, ((it / kStages) & 1u) ^ 1u, gw, 1)) {
             // giving up: let the loads already issued land before the CTA (and its shared memory) goes away
-            for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; back++) {
-              const uint32_t j = it - back;
-              uint32_t spins = 0;
-              while (!mbar_test(full + (j % kStages), (j / kStages) & 1u) && ++spins < (1u << 20)) {}
+            if (leads) {
+              for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; back++) {
+                const uint32_t j = it - back;
+                uint32_t spins = 0;
+                while (!mbar_test(full + (j % kStages), (j / kStages) & 1u) && ++spins < (1u << 20)) {}
+              }
+            } else {
+              for (int w = 0; w < 2000; w++) __nanosleep(1000);   // its loads complete under the leader's barriers: 2 ms
             }
             goto done;
           }
-          mbar_arrive_expect(full + s, kStageBytes);
-          tma_load_2d(ring + s * kStageBytes, &map_a, kb * kBK, m0, full + s);
-          tma_load_2d(ring + s * kStageBytes + kABytes, &map_b, kb * kBK, n0, full + s);
+          if constexpr (G == 2) {
+            // both CTAs' bytes are counted under the leader's barrier; only the leader announces them
+            const uint32_t lead_full = cluster_addr(full + s, 0u);
+            if (leads) mbar_arrive_expect(full + s, S::kTxBytes);
+            tma_load_2d_pair(ring + s * kStageBytes, &map_a, kb * kBK, m0 + (int)crank * kBM, lead_full);
+            tma_load_2d_pair(ring + s * kStageBytes + kABytes, &map_b, kb * kBK, n0 + (int)crank * (BN / 2), lead_full);
+          } else {
+            mbar_arrive_expect(full + s, kStageBytes);
+            tma_load_2d(ring + s * kStageBytes, &map_a, kb * kBK, m0, full + s);
+            tma_load_2d(ring + s * kStageBytes + kABytes, &map_b, kb * kBK, n0, full + s);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (of a pair: the leader's)
+    if (lane == 0 && leads) {
       uint32_t it = 0, tile_i = 0;
-      SegIter seg(p.stream_k, tiles, kblocks);
+      SegIter seg(p.stream_k, tiles, kblocks, unit, units);
       Seg sg;
       for (; seg.next(sg); tile_i++) {
         const uint32_t a = tile_i & 1u;
@@ -332,11 +400,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const uint64_t da = umma_desc_k128(ring + s * kStageBytes);
           const uint64_t db = umma_desc_k128(ring + s * kStageBytes + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; k++)
-            umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (j | k) != 0 ? 1u : 0u);
-          umma_commit(empty + s);          // the stage is free once these MMAs have read it
+          for (int k = 0; k < kBK / 16; k++) {
+            if constexpr (G == 2) umma_bf16_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (j | k) != 0 ? 1u : 0u);
+            else umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), kIdesc, (j | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free once these MMAs have read it (of a pair: in both CTAs)
+          if constexpr (G == 2) umma_commit_pair(empty + s); else umma_commit(empty + s);
         }
-        umma_commit(acc_full + a);         // the accumulator is complete once everything above has run
+        // the accumulator is complete once everything above has run
+        if constexpr (G == 2) umma_commit_pair(acc_full + a); else umma_commit(acc_full + a);
       }
     }
   } else {
@@ -347,15 +419,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const size_t buf_off = p.nranks ? (size_t)(*p.call_counter & 1u) * p.buf_bytes : 0;
     const int qrow_bytes = p.N / 2 + p.N / 16;
     uint32_t tile_i = 0;
-    SegIter seg(p.stream_k, tiles, kblocks);
+    SegIter seg(p.stream_k, tiles, kblocks, unit, units);
     Seg sg;
     // this thread's float4 i of chunk c inside a partial slot: a warp's 32 rows are 512 contiguous bytes
     auto slot_ptr = [&](int cta, int c, int i) {
       return reinterpret_cast<float4*>(p.sk_partial) + ((size_t)cta * (BN / 32) + c) * 8 * kBM + (size_t)i * kBM + r_in_tile;
     };
+    // 128 arrivals per CTA hand the accumulator back to the MMA warp (of a pair: to the leader's)
+    auto hand_back = [&](uint32_t a) {
+      if constexpr (G == 2) mbar_arrive_cluster(cluster_addr(acc_empty + a, 0u)); else mbar_arrive(acc_empty + a);
+    };
     for (; seg.next(sg); tile_i++) {
       int m0, n0;
-      tile_coords<BN>(sg.tile, m_tiles, n_tiles, m0, n0);
+      tile_coords<BN, G>(sg.tile, m_tiles, n_tiles, m0, n0);
+      m0 += (int)crank * kBM;                              // of a pair: this CTA's half of the 256 rows
       const uint32_t a = tile_i & 1u;
       const int row = m0 + r_in_tile;
       const bool produces = sg.kind == kProduce;           // a share of the tile's K blocks: leave a partial
@@ -379,17 +456,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           for (int i = 0; i < 8; i++) *slot_ptr(blockIdx.x, c, i) = make_float4(vc[4 * i], vc[4 * i + 1], vc[4 * i + 2], vc[4 * i + 3]);
         }
         tc_fence_before();
-        mbar_arrive(acc_empty + a);
+        hand_back(a);
         __syncwarp();
         if (lane == 0) { __threadfence(); st_release_gpu(flag, 1u); }
         continue;
       }
       float pv[2][32];
-      uint32_t* fix_flag = p.sk_flags + (blockIdx.x + 1) * 4 + q;
+      uint32_t* fix_flag = p.sk_flags + (blockIdx.x + G) * 4 + q;
       auto load_partial = [&](int c, float* dst) {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-          const float4 f = __ldcg(slot_ptr(blockIdx.x + 1, c, i));
+          const float4 f = __ldcg(slot_ptr(blockIdx.x + G, c, i));
           dst[4 * i] = f.x; dst[4 * i + 1] = f.y; dst[4 * i + 2] = f.z; dst[4 * i + 3] = f.w;
         }
       };
@@ -434,7 +511,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (lane == 0) st_release_gpu(fix_flag, 0u);        // every lane has its partial in registers: the slot is free
       }
       tc_fence_before();
-      mbar_arrive(acc_empty + a);                 // 128 arrivals hand the accumulator back to the MMA warp
+      hand_back(a);                 // 128 arrivals hand the accumulator back to the MMA warp
       fence_smem_to_async();
       if (row < p.M) {
         const size_t voff = (size_t)(n0 / 2), soff = (size_t)(p.N / 2 + n0 / 16);
@@ -468,7 +545,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 done:
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if constexpr (G == 2) cluster_sync_all();   // neither CTA frees TMEM or leaves while the other's MMAs, commits or arrivals may still touch it
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    if constexpr (G == 2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ---- host side ----
@@ -537,15 +619,32 @@ static bool stream_k_space(int slots, StreamKSpace* out) {
 
 using namespace fp4ar;
 
-template <int BN>
+template <int BN, int G>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
-  using S = GemmShape<BN>;
-  if (cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmem) != cudaSuccess) return cuda_fail();
-  const int tiles = (p.N / BN) * ((p.M + kBM - 1) / kBM);
+  using S = GemmShape<BN, G>;
+  if (cudaFuncSetAttribute(gemm_nvfp4_kernel<BN, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmem) != cudaSuccess) return cuda_fail();
+  const int tiles = (p.N / BN) * ((p.M + kBM * G - 1) / (kBM * G));
   const int sms = device_sm_count();
-  const int grid = tiles < sms ? tiles : sms;
-  if (p.stream_k && grid != sms) return FP4AR_ERR_ARGUMENT;      // the split needs tiles >= CTAs, one CTA per SM
-  gemm_nvfp4_kernel<BN><<<grid, kGemmThreads, S::kSmem, stream>>>(ma, mb, p);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int units = sms / G;
+  if (G == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.gridDim = dim3(sms & ~1);
+    int clusters = 0;      // pairs that can be resident together: the grid is persistent, every pair must be
+    if (cudaOccupancyMaxActiveClusters(&clusters, gemm_nvfp4_kernel<BN, G>, &cfg) != cudaSuccess || clusters < 1) return cuda_fail();
+    if (clusters < units) units = clusters;
+  }
+  if (tiles < units) units = tiles;
+  if (p.stream_k && (tiles <= units || tiles % units == 0)) return FP4AR_ERR_ARGUMENT;      // see SegIter
+  cfg.gridDim = dim3(units * G);
+  if (cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<BN, G>, ma, mb, p) != cudaSuccess) return cuda_fail();
   return cuda_check_launch();
 }
 
@@ -558,7 +657,7 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   // about 0.87 of the per-cycle work of a 256-wide one (M = 4096: 321 vs 315 us at K = 8192 although its last wave
   // is full), so it is only taken where it wins clearly (M = 1024: 111 vs 123 us); N must be a multiple of 192 too.
   int bn = 256;
-  bool stream_k = false;
+  bool stream_k = false, pair = false;
   {
     const char* force = std::getenv("FP4AR_GEMM_TILE_N");
     const int sms = device_sm_count();
@@ -579,6 +678,20 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
     const char* fsk = std::getenv("FP4AR_GEMM_STREAM_K");
     if (fsk) stream_k = std::atoi(fsk) != 0 && tiles256 > sms && tiles256 % sms != 0;
     if (stream_k) bn = 256;
+    // CTA pairs (tcgen05 cta_group::2) where the K loop is long or there are many tiles: measured against single CTAs
+    // at M = 1024 / 2048 / 4096 / 16384: K = 8192: 80 / 131 / 252 / 1054 us against 88 / 143 / 268 / 1078; K = 4096:
+    // 52 / 76 / 135 / 506 against 53 / 78 / 137 / 524; K = 2048: 35 / 49 / 80 / 260 against 33 / 47 / 78 / 266.
+    // FP4AR_GEMM_PAIR = 0 / 1 overrides.
+    const char* fp = std::getenv("FP4AR_GEMM_PAIR");
+    const bool want_pair = fp ? std::atoi(fp) != 0 : ((K >= 4096 || M >= 8192) && !force);
+    if (want_pair && sms >= 2) {
+      pair = true; bn = 256;
+      const int units = sms / 2;
+      const long tiles2 = (long)(N / 256) * ((M + 2 * kBM - 1) / (2 * kBM));
+      const double busy2 = (double)tiles2 / (double)(((tiles2 + units - 1) / units) * units);
+      stream_k = tiles2 > units && tiles2 % units != 0 && busy2 < 0.95 && (K >= 4096 || tiles2 >= 4 * units);
+      if (fsk) stream_k = std::atoi(fsk) != 0 && tiles2 > units && tiles2 % units != 0;
+    }
   }
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -606,8 +719,9 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
     if (stream_k_space(device_sm_count(), &sp)) { p.stream_k = 1; p.sk_partial = sp.partial; p.sk_flags = sp.flags; }
   }
   CUtensorMap ma, mb;
-  if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, bn)) return FP4AR_ERR_UNSUPPORTED;
-  return bn == 192 ? launch_gemm<192>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256>(ma, mb, p, (cudaStream_t)stream);
+  if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, pair ? bn / 2 : bn)) return FP4AR_ERR_UNSUPPORTED;
+  if (pair) return launch_gemm<256, 2>(ma, mb, p, (cudaStream_t)stream);
+  return bn == 192 ? launch_gemm<192, 1>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256, 1>(ma, mb, p, (cudaStream_t)stream);
 }
 
 extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {

@@ -21,8 +21,10 @@ def _xw(M, K, Nn, seed):
     return x, wt
 
 
+@pytest.mark.parametrize("pair", [0, 1])
 @pytest.mark.parametrize("M,K,Nn", [(128, 64, 256), (300, 512, 512), (1024, 2048, 6144), (77, 4096, 6144)])
-def test_gemm_accumulators_and_quantised_rows(M, K, Nn):
+def test_gemm_accumulators_and_quantised_rows(M, K, Nn, pair, monkeypatch):
+    monkeypatch.setenv("FP4AR_GEMM_PAIR", str(pair))      # 1: two CTAs per 256 x 256 tile (tcgen05 cta_group::2)
     x, wt = _xw(M, K, Nn, 1)
     gs = G.calibrate_gs(x, wt)
     q, acc = G.gemm_nvfp4(x, wt, gs, want_acc=True)
@@ -69,8 +71,9 @@ def test_gemm_push_then_allreduce_on_emulated_ranks(P):
     g.close()
 
 
+@pytest.mark.parametrize("pair", [0, 1])
 @pytest.mark.parametrize("M,K", [(1024, 2048), (2048, 512), (1000, 1024), (2300, 320)])
-def test_gemm_stream_k_split(M, K, monkeypatch):
+def test_gemm_stream_k_split(M, K, pair, monkeypatch):
     """Tile counts that do not fill the last wave of CTAs run with the K loop cut into equal ranges per CTA: a tile shared
     by two CTAs is summed from a partial accumulator.  Same checks as for whole tiles, over several calls (the partial
     slots and their flags are reused), inside a CUDA graph of back-to-back launches, and against the whole-tile walk."""
@@ -79,6 +82,7 @@ def test_gemm_stream_k_split(M, K, monkeypatch):
     gs = G.calibrate_gs(x, wt)
     ref = x.float() @ wt.float().t()
     tol = 2e-3 * ref.abs().max().item() + 1e-4
+    monkeypatch.setenv("FP4AR_GEMM_PAIR", str(pair))
     monkeypatch.setenv("FP4AR_GEMM_STREAM_K", "0")
     q_plain, acc_plain = G.gemm_nvfp4(x, wt, gs, want_acc=True)
     torch.cuda.synchronize()
