@@ -8,16 +8,22 @@
 //                 where the AllReduce kernel in "pushed input" mode finds them, and/or
 //               - into a local [M, N/2 + N/16] NVFP4 tensor.
 //
-// sm_100a structure: persistent CTAs (one per SM), 128 x 256 output tiles, K in blocks of 64.  Where the tile count is
-// not a multiple of the CTA count, the first (CTAs + remainder) tiles are cut along K into equal ranges per CTA
-// (stream-K, see SegIter) so that no CTA idles through a last wave; 128 x 192 tiles are the fallback where that does
-// not apply (fewer tiles than CTAs).
-//   warp 0  : TMA producer   - cp.async.bulk.tensor (plain per-CTA loads) of the A and B blocks into a 4-stage ring,
-//                              128-byte swizzle, completion on mbarriers
-//   warp 1  : MMA issuer     - one thread issues tcgen05.mma (cta_group::1, kind::f16, M128 N256 K16) from
+// sm_100a structure: persistent CTAs (one per SM), K in blocks of 64, three shapes:
+//   pairs  (default for K >= 4096 or M >= 8192): the two CTAs of a cluster share one 256 x 256 tile with tcgen05
+//          cta_group::2: each loads its own 128 rows of A and half of the B block into a 6-stage ring, the even CTA
+//          issues the MMAs for both, each CTA's TMEM holds the accumulator of its own 128 rows;
+//   single: one CTA per 128 x 256 tile (4-stage ring) or 128 x 192 tile (5-stage ring, where that fills the last wave
+//          of CTAs better and the K split below does not apply).
+// Where the tile count is not a multiple of the unit count (CTAs or pairs), the first (units + remainder) tiles are cut
+// along K into equal ranges per unit (stream-K, see SegIter) so that no SM idles through a last wave.
+//   warp 0  : TMA producer   - cp.async.bulk.tensor (every CTA loads for itself) of the A and B blocks into the ring,
+//                              128-byte swizzle, completion on mbarriers (of a pair: both CTAs' bytes are counted
+//                              under the leader's barrier)
+//   warp 1  : MMA issuer     - one thread issues tcgen05.mma (kind::f16, M 128 per CTA, N 256, K 16) from
 //                              shared-memory descriptors into TMEM; tcgen05.commit releases ring stages and
-//                              publishes finished accumulators; owns tcgen05.alloc / dealloc (512 columns =
-//                              two accumulators, so the epilogue of tile i overlaps the main loop of tile i+1)
+//                              publishes finished accumulators (of a pair: on both CTAs' barriers); owns
+//                              tcgen05.alloc / dealloc (512 columns = two accumulators, so the epilogue of tile i
+//                              overlaps the main loop of tile i+1)
 //   warps 2-5: epilogue      - tcgen05.ld (32 lanes x 32 columns per instruction), quantise, stage the row
 //                              pieces in shared memory, bulk-store them to the (peer) windows
 // Every wait is bounded; a wait that gives up raises a CTA-wide abort flag, the roles drain, TMEM is freed and
@@ -126,7 +132,7 @@ __device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t ran
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
-// TMA load of one CTA of a pair: the bytes are counted under the barrier at `cluster_bar` (the leader's), no multicast
+// TMA load of one CTA of a pair: the bytes are counted under the barrier at `cluster_bar` (the leader's); every CTA loads for itself
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
