@@ -37,8 +37,10 @@ def test_gemm_accumulators_and_quantised_rows(M, K, Nn, pair, monkeypatch):
     assert np.count_nonzero(q.cpu().numpy() != want) == 0
 
 
+@pytest.mark.parametrize("pair", [0, 1])
 @pytest.mark.parametrize("P", [2, 4])
-def test_gemm_push_then_allreduce_on_emulated_ranks(P):
+def test_gemm_push_then_allreduce_on_emulated_ranks(P, pair, monkeypatch):
+    monkeypatch.setenv("FP4AR_GEMM_PAIR", str(pair))
     M, K = 256, 512
     g = EmulatedGroup(P, M)
     g.set_timeout_ms(500)
