@@ -338,8 +338,8 @@ extern "C" int fp4ar_launch(fp4ar_ctx* c, const fp4ar_args* args, fp4ar_stream s
   // at large row counts and the shallow pipeline wins; (2,3) at eight, where every row waits on seven peers and one
   // more step of slack at each hand-off pays at every row count (16K rows: 284 -> 228 us).  A step of a six-warp team
   // takes about half as long, so those shapes run (2,3) everywhere.  Eight GPUs, 16384 rows, AR / block: (2,3) 179 /
-  // 238 us, (2,4) 192 / 240, (3,4) 181 / 240; 1024 rows: 24.6, 27.6, 23.2 us.  Four emulated ranks x 4096 rows on one
-  // GPU: (1,2) 191 us, (2,3) 142, (2,4) 139, (3,4) 141.
+  // 238 us, (2,4) 192 / 240, (3,4) 181 / 240; 1024 rows: 24.6, 27.6, 23.2 us.  Four GPUs, 16384 rows: (1,2) 209 / 231,
+  // (2,3) 150 / 199, (2,4) 156 / 202, (3,4) 154 / 201; 1024 rows: 23.6, 17.8, 18.8, 18.6 us.
   {
     int lo = a0.tune[3] & 15, lf = (a0.tune[3] >> 4) & 15;
     if (lo < 1 || lf <= lo || lf > 4) {
