@@ -636,16 +636,28 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = S::kSmem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int units = sms / G;
+  cfg.attrs = attr;
   if (G == 2) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.numAttrs = 1;
     cfg.gridDim = dim3(sms & ~1);
     int clusters = 0;      // pairs that can be resident together: the grid is persistent, every pair must be
     if (cudaOccupancyMaxActiveClusters(&clusters, gemm_nvfp4_kernel<BN, G>, &cfg) != cudaSuccess || clusters < 1) return cuda_fail();
     if (clusters < units) units = clusters;
+  }
+  // Programmatic dependent launch: a CTA may start (barrier set-up, TMEM allocation) on an SM that the previous
+  // kernel's CTA has left while other CTAs of that kernel still run; it touches global memory only after
+  // griddepcontrol.wait.  FP4AR_GEMM_PDL = 0 turns it off.
+  {
+    const char* e = std::getenv("FP4AR_GEMM_PDL");
+    if (!e || std::atoi(e) != 0) {
+      attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+      cfg.numAttrs++;
+    }
   }
   if (tiles < units) units = tiles;
   if (p.stream_k && (tiles <= units || tiles % units == 0)) return FP4AR_ERR_ARGUMENT;      // see SegIter
