@@ -129,6 +129,8 @@ def cuda() -> C.CDLL:
     lib.fp4ar_gemm_nvfp4.restype = C.c_int
     lib.fp4ar_gemm_status.argtypes = [C.POINTER(StatusWords)]
     lib.fp4ar_gemm_status.restype = C.c_int
+    lib.fp4ar_gemm_reset.argtypes = []
+    lib.fp4ar_gemm_reset.restype = C.c_int
     for name in ("fp4ar_create", "fp4ar_create_emulated", "fp4ar_launch", "fp4ar_status", "fp4ar_set_timeout_ms",
                  "fp4ar_reset", "fp4ar_destroy", "fp4ar_get_push_view", "fp4ar_ctas_per_rank", "fp4ar_encode",
                  "fp4ar_encode_static", "fp4ar_decode_sum", "fp4ar_reduce_reencode", "fp4ar_add_rmsnorm",

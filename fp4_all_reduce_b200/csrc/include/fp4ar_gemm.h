@@ -25,6 +25,9 @@ int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const void* x, c
                      float gs, void* local_q, float* dbg_acc, fp4ar_stream stream);
 /* Status block of the GEMM kernels on the current device (code != 0: a bounded wait gave up). */
 int fp4ar_gemm_status(fp4ar_status_words* out);
+/* After a GEMM whose status is not 0: waits for the device, then clears the status block and the hand-off flags of the
+ * partial tiles that such a launch may have left set (a later launch would wait on them until its limit). */
+int fp4ar_gemm_reset(void);
 
 #ifdef __cplusplus
 }

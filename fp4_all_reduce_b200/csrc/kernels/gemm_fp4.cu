@@ -601,9 +601,11 @@ static StatusWords* gemm_status_word() {
 // first call on a device and kept (19 MB on a B200).  Launches that share a device take turns on a slot through its
 // flags: a producer waits until the consumer of the previous launch has reset them.
 struct StreamKSpace { float* partial; uint32_t* flags; int slots; };
+static StreamKSpace g_stream_k_space[64] = {};
+static std::mutex g_stream_k_mu;
 static bool stream_k_space(int slots, StreamKSpace* out) {
-  static StreamKSpace sp[64] = {};
-  static std::mutex mu;
+  StreamKSpace* sp = g_stream_k_space;
+  std::mutex& mu = g_stream_k_mu;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   std::lock_guard<std::mutex> g(mu);
@@ -740,6 +742,22 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, pair ? bn / 2 : bn)) return FP4AR_ERR_UNSUPPORTED;
   if (pair) return launch_gemm<256, 2>(ma, mb, p, (cudaStream_t)stream);
   return bn == 192 ? launch_gemm<192, 1>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256, 1>(ma, mb, p, (cudaStream_t)stream);
+}
+
+extern "C" int fp4ar_gemm_reset(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cuda_fail();
+  if (cudaDeviceSynchronize() != cudaSuccess) return cuda_fail();
+  StatusWords* s = gemm_status_word();
+  if (!s) return cuda_fail();
+  if (cudaMemset(s, 0, sizeof(StatusWords)) != cudaSuccess) return cuda_fail();
+  {
+    std::lock_guard<std::mutex> g(g_stream_k_mu);
+    const StreamKSpace& sp = g_stream_k_space[dev];
+    if (sp.flags && cudaMemset(sp.flags, 0, (size_t)sp.slots * 4 * sizeof(uint32_t)) != cudaSuccess) return cuda_fail();
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return cuda_fail();
+  return FP4AR_OK;
 }
 
 extern "C" int fp4ar_gemm_status(fp4ar_status_words* out) {

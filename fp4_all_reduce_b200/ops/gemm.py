@@ -97,3 +97,9 @@ def gemm_status() -> N.StatusWords:
     w = N.StatusWords()
     N.check(N.cuda().fp4ar_gemm_status(C.byref(w)), "fp4ar_gemm_status")
     return w
+
+
+def gemm_reset() -> None:
+    """After a GEMM whose status is not 0: synchronise, clear the status block and the hand-off flags of the partial
+    tiles, so that later launches do not wait on what the failed one left behind."""
+    N.check(N.cuda().fp4ar_gemm_reset(), "fp4ar_gemm_reset")

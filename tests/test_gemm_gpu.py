@@ -117,3 +117,14 @@ def test_gemm_stream_k_split(M, K, pair, monkeypatch):
         assert G.gemm_status().code == 0
         for o in outs:
             assert torch.equal(o, first)
+
+
+def test_gemm_reset_keeps_the_kernel_usable():
+    x, wt = _xw(1024, 2048, N.HIDDEN, 5)
+    gs = G.calibrate_gs(x, wt)
+    q0 = G.gemm_nvfp4(x, wt, gs)
+    G.gemm_reset()
+    assert G.gemm_status().code == 0
+    q1 = G.gemm_nvfp4(x, wt, gs)
+    torch.cuda.synchronize()
+    assert G.gemm_status().code == 0 and torch.equal(q0, q1)
