@@ -129,6 +129,9 @@ def cuda() -> C.CDLL:
     lib.fp4ar_gemm_nvfp4.restype = C.c_int
     lib.fp4ar_gemm_status.argtypes = [C.POINTER(StatusWords)]
     lib.fp4ar_gemm_status.restype = C.c_int
+    ip = C.POINTER(C.c_int)
+    lib.fp4ar_gemm_plan.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, ip, ip, ip, ip, ip, C.c_int, ip, C.c_int]
+    lib.fp4ar_gemm_plan.restype = C.c_int
     lib.fp4ar_gemm_reset.argtypes = []
     lib.fp4ar_gemm_reset.restype = C.c_int
     for name in ("fp4ar_create", "fp4ar_create_emulated", "fp4ar_launch", "fp4ar_status", "fp4ar_set_timeout_ms",

@@ -28,6 +28,13 @@ int fp4ar_gemm_status(fp4ar_status_words* out);
 /* After a GEMM whose status is not 0: waits for the device, then clears the status block and the hand-off flags of the
  * partial tiles that such a launch may have left set (a later launch would wait on them until its limit). */
 int fp4ar_gemm_reset(void);
+/* The schedule a call of this size takes on a device with `sms` SMs (host only, no device work; environment overrides
+ * are not applied): CTA pairs or single CTAs, tile width, whether the K loop is cut across units (stream-K), how many
+ * units (CTAs or pairs) work on how many tiles.  With `segments` != NULL also the work list of unit `unit` as
+ * quadruples (tile, first K block, K blocks, kind: 0 whole tile, 1 leaves a partial, 2 adds the next unit's partial);
+ * returns the number of segments (also when it exceeds max_segments), 0 without a list, -1 for bad arguments. */
+int fp4ar_gemm_plan(int M, int N, int K, int sms, int* pair, int* tile_n, int* stream_k, int* units, int* tiles,
+                    int unit, int* segments, int max_segments);
 
 #ifdef __cplusplus
 }

@@ -275,7 +275,7 @@ struct SegIter {
   int tiles, kblocks, stride, t;
   long long u, u_end;
   // unit = this CTA (or CTA pair) among `units` of them
-  __device__ SegIter(int stream_k, int tiles_, int kblocks_, int unit, int units) : tiles(tiles_), kblocks(kblocks_), stride(units) {
+  __host__ __device__ SegIter(int stream_k, int tiles_, int kblocks_, int unit, int units) : tiles(tiles_), kblocks(kblocks_), stride(units) {
     const int g = units;
     const int cut_tiles = stream_k ? g + tiles_ % g : 0;
     const long long total = (long long)cut_tiles * kblocks_;
@@ -283,7 +283,7 @@ struct SegIter {
     u_end = total * (unit + 1) / g;
     t = cut_tiles + unit;
   }
-  __device__ bool next(Seg& s) {
+  __host__ __device__ bool next(Seg& s) {
     if (u < u_end) {
       s.tile = (int)(u / kblocks);
       const int off = (int)(u - (long long)s.tile * kblocks);
@@ -627,8 +627,55 @@ static bool stream_k_space(int slots, StreamKSpace* out) {
 
 using namespace fp4ar;
 
+// Which shape a call takes.  `units` = CTAs (or CTA pairs) that work, `tiles` = output tiles of that shape.
+struct GemmPlan { int pair, bn, stream_k, units, tiles; };
+static GemmPlan plan_gemm(int M, int N, int K, int sms, bool env) {
+  // Tile width of single CTAs: the one whose tiles keep the persistent CTAs busier over all waves.  A 192-wide tile was
+  // measured at about 0.87 of the per-cycle work of a 256-wide one (M = 4096: 321 vs 315 us at K = 8192 although its
+  // last wave is full), so it is only taken where it wins clearly (M = 1024: 111 vs 123 us); N must be a multiple of
+  // 192 too.  FP4AR_GEMM_TILE_N = 192 / 256 forces it (and single CTAs).
+  int bn = 256;
+  bool stream_k = false, pair = false;
+  const char* force = env ? std::getenv("FP4AR_GEMM_TILE_N") : nullptr;
+  const char* fsk = env ? std::getenv("FP4AR_GEMM_STREAM_K") : nullptr;
+  const char* fp = env ? std::getenv("FP4AR_GEMM_PAIR") : nullptr;
+  auto busy = [&](int w) {
+    const long tiles = (long)(N / w) * ((M + kBM - 1) / kBM);
+    return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
+  };
+  if (N % 192 == 0 && 0.80 * busy(192) > busy(256)) bn = 192;
+  if (force && std::atoi(force) == 256) bn = 256;
+  if (force && std::atoi(force) == 192 && N % 192 == 0) bn = 192;
+  // Stream-K (256-wide tiles, the K loop cut into equal ranges per CTA) where whole tiles would leave the last wave
+  // of CTAs partly idle and the K loop is long enough to pay for the partial sums (K = 2048: 36.9 us against 33.0 us
+  // with whole 192-wide tiles at M = 1024, level at M = 2048, 77.8 against 79.9 at M = 4096; K = 8192: 86 / 143 /
+  // 264 us against 96 / 154 / 296 at M = 1024 / 2048 / 4096); FP4AR_GEMM_STREAM_K = 0 / 1 overrides.
+  const long tiles256 = (long)(N / 256) * ((M + kBM - 1) / kBM);
+  stream_k = tiles256 > sms && tiles256 % sms != 0 && busy(256) < 0.95 && (K >= 4096 || tiles256 >= 4 * sms) &&
+             !(force && std::atoi(force) == 192);
+  if (fsk) stream_k = std::atoi(fsk) != 0 && tiles256 > sms && tiles256 % sms != 0;
+  if (stream_k) bn = 256;
+  // CTA pairs (tcgen05 cta_group::2) where the K loop is long or there are many tiles: measured against single CTAs
+  // at M = 1024 / 2048 / 4096 / 16384: K = 8192: 80 / 131 / 252 / 1054 us against 88 / 143 / 268 / 1078; K = 4096:
+  // 52 / 76 / 135 / 506 against 53 / 78 / 137 / 524; K = 2048: 35 / 49 / 80 / 260 against 33 / 47 / 78 / 266.
+  // FP4AR_GEMM_PAIR = 0 / 1 overrides.
+  const bool want_pair = fp ? std::atoi(fp) != 0 : ((K >= 4096 || M >= 8192) && !force);
+  long tiles = (long)(N / bn) * ((M + kBM - 1) / kBM);
+  int units = sms;
+  if (want_pair && sms >= 2) {
+    pair = true; bn = 256;
+    units = sms / 2;
+    tiles = (long)(N / 256) * ((M + 2 * kBM - 1) / (2 * kBM));
+    const double busy2 = (double)tiles / (double)(((tiles + units - 1) / units) * units);
+    stream_k = tiles > units && tiles % units != 0 && busy2 < 0.95 && (K >= 4096 || tiles >= 4 * units);
+    if (fsk) stream_k = std::atoi(fsk) != 0 && tiles > units && tiles % units != 0;
+  }
+  if (tiles < units) units = (int)tiles;
+  return GemmPlan{pair ? 1 : 0, bn, stream_k ? 1 : 0, units, (int)tiles};
+}
+
 template <int BN, int G>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t stream) {
   using S = GemmShape<BN, G>;
   if (cudaFuncSetAttribute(gemm_nvfp4_kernel<BN, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmem) != cudaSuccess) return cuda_fail();
   const int tiles = (p.N / BN) * ((p.M + kBM * G - 1) / (kBM * G));
@@ -662,7 +709,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     }
   }
   if (tiles < units) units = tiles;
-  if (p.stream_k && (tiles <= units || tiles % units == 0)) return FP4AR_ERR_ARGUMENT;      // see SegIter
+  if (p.stream_k && (tiles <= units || tiles % units == 0)) p.stream_k = 0;      // fewer units fit than planned: whole tiles (see SegIter)
   cfg.gridDim = dim3(units * G);
   if (cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<BN, G>, ma, mb, p) != cudaSuccess) return cuda_fail();
   return cuda_check_launch();
@@ -673,46 +720,9 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   if (!x || !wt || M < 1 || N < 256 || K < kBK || (N % 256) || (K % kBK) || !(gs > 0.0f)) return FP4AR_ERR_ARGUMENT;
   if (((uintptr_t)x | (uintptr_t)wt | (uintptr_t)local_q | (uintptr_t)dbg_acc) & 15) return FP4AR_ERR_ARGUMENT;
   if (!push && !local_q && !dbg_acc) return FP4AR_ERR_ARGUMENT;
-  // Tile width: the one whose tiles keep the persistent CTAs busier over all waves.  A 192-wide tile was measured at
-  // about 0.87 of the per-cycle work of a 256-wide one (M = 4096: 321 vs 315 us at K = 8192 although its last wave
-  // is full), so it is only taken where it wins clearly (M = 1024: 111 vs 123 us); N must be a multiple of 192 too.
-  int bn = 256;
-  bool stream_k = false, pair = false;
-  {
-    const char* force = std::getenv("FP4AR_GEMM_TILE_N");
-    const int sms = device_sm_count();
-    auto busy = [&](int w) {
-      const long tiles = (long)(N / w) * ((M + kBM - 1) / kBM);
-      return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms);
-    };
-    if (N % 192 == 0 && 0.80 * busy(192) > busy(256)) bn = 192;
-    if (force && std::atoi(force) == 256) bn = 256;
-    if (force && std::atoi(force) == 192 && N % 192 == 0) bn = 192;
-    // Stream-K (256-wide tiles, the K loop cut into equal ranges per CTA) where whole tiles would leave the last wave
-    // of CTAs partly idle and the K loop is long enough to pay for the partial sums (K = 2048: 36.9 us against 33.0 us
-    // with whole 192-wide tiles at M = 1024, level at M = 2048, 77.8 against 79.9 at M = 4096; K = 8192: 86 / 143 /
-    // 264 us against 96 / 154 / 296 at M = 1024 / 2048 / 4096); FP4AR_GEMM_STREAM_K = 0 / 1 overrides.
-    const long tiles256 = (long)(N / 256) * ((M + kBM - 1) / kBM);
-    stream_k = tiles256 > sms && tiles256 % sms != 0 && busy(256) < 0.95 && (K >= 4096 || tiles256 >= 4 * sms) &&
-               !(force && std::atoi(force) == 192);
-    const char* fsk = std::getenv("FP4AR_GEMM_STREAM_K");
-    if (fsk) stream_k = std::atoi(fsk) != 0 && tiles256 > sms && tiles256 % sms != 0;
-    if (stream_k) bn = 256;
-    // CTA pairs (tcgen05 cta_group::2) where the K loop is long or there are many tiles: measured against single CTAs
-    // at M = 1024 / 2048 / 4096 / 16384: K = 8192: 80 / 131 / 252 / 1054 us against 88 / 143 / 268 / 1078; K = 4096:
-    // 52 / 76 / 135 / 506 against 53 / 78 / 137 / 524; K = 2048: 35 / 49 / 80 / 260 against 33 / 47 / 78 / 266.
-    // FP4AR_GEMM_PAIR = 0 / 1 overrides.
-    const char* fp = std::getenv("FP4AR_GEMM_PAIR");
-    const bool want_pair = fp ? std::atoi(fp) != 0 : ((K >= 4096 || M >= 8192) && !force);
-    if (want_pair && sms >= 2) {
-      pair = true; bn = 256;
-      const int units = sms / 2;
-      const long tiles2 = (long)(N / 256) * ((M + 2 * kBM - 1) / (2 * kBM));
-      const double busy2 = (double)tiles2 / (double)(((tiles2 + units - 1) / units) * units);
-      stream_k = tiles2 > units && tiles2 % units != 0 && busy2 < 0.95 && (K >= 4096 || tiles2 >= 4 * units);
-      if (fsk) stream_k = std::atoi(fsk) != 0 && tiles2 > units && tiles2 % units != 0;
-    }
-  }
+  const GemmPlan pl = plan_gemm(M, N, K, device_sm_count(), /*env=*/true);
+  const int bn = pl.bn;
+  const bool stream_k = pl.stream_k != 0, pair = pl.pair != 0;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.inv_gs = 1.0f / gs;
@@ -742,6 +752,26 @@ extern "C" int fp4ar_gemm_nvfp4(const fp4ar_push_view* push, int two_shot, const
   if (!make_map(&ma, x, M, K, kBM) || !make_map(&mb, wt, N, K, pair ? bn / 2 : bn)) return FP4AR_ERR_UNSUPPORTED;
   if (pair) return launch_gemm<256, 2>(ma, mb, p, (cudaStream_t)stream);
   return bn == 192 ? launch_gemm<192, 1>(ma, mb, p, (cudaStream_t)stream) : launch_gemm<256, 1>(ma, mb, p, (cudaStream_t)stream);
+}
+
+// The schedule of one launch, computed on the host with the kernel's own iterator (for tests and tools): which shape
+// a call of this size takes, and the segments of one unit as (tile, first K block, K blocks, kind) quadruples.
+extern "C" int fp4ar_gemm_plan(int M, int N, int K, int sms, int* pair, int* tile_n, int* stream_k, int* units, int* tiles,
+                               int unit, int* segments, int max_segments) {
+  if (M < 1 || N < 256 || K < kBK || (N % 256) || (K % kBK) || sms < 2 || !pair || !tile_n || !stream_k || !units || !tiles)
+    return -1;
+  GemmPlan pl = plan_gemm(M, N, K, sms, /*env=*/false);
+  *pair = pl.pair; *tile_n = pl.bn; *stream_k = pl.stream_k; *units = pl.units; *tiles = pl.tiles;
+  if (!segments) return 0;
+  if (unit < 0 || unit >= pl.units) return -1;
+  SegIter it(pl.stream_k, pl.tiles, K / kBK, unit, pl.units);
+  Seg sg;
+  int n = 0;
+  while (it.next(sg)) {
+    if (n < max_segments) { segments[4 * n] = sg.tile; segments[4 * n + 1] = sg.lo; segments[4 * n + 2] = sg.count; segments[4 * n + 3] = sg.kind; }
+    n++;
+  }
+  return n;
 }
 
 extern "C" int fp4ar_gemm_reset(void) {

@@ -103,3 +103,27 @@ def gemm_reset() -> None:
     """After a GEMM whose status is not 0: synchronise, clear the status block and the hand-off flags of the partial
     tiles, so that later launches do not wait on what the failed one left behind."""
     N.check(N.cuda().fp4ar_gemm_reset(), "fp4ar_gemm_reset")
+
+
+def gemm_plan(M: int, Nn: int, K: int, sms: int = 148, unit: Optional[int] = None):
+    """The schedule a GEMM of this size takes on a device with `sms` SMs (host only): a dict with `pair`, `tile_n`,
+    `stream_k`, `units`, `tiles`, and with `unit` given also `segments`: the work list of that unit as
+    (tile, first K block, K blocks, kind) tuples; kind 0 whole tile, 1 leaves a partial, 2 adds the next unit's."""
+    vals = [C.c_int() for _ in range(5)]
+    lib = N.cuda()
+    rc = lib.fp4ar_gemm_plan(M, Nn, K, sms, *[C.byref(v) for v in vals], 0, None, 0)
+    if rc < 0:
+        raise ValueError("unsupported GEMM shape")
+    out = dict(zip(("pair", "tile_n", "stream_k", "units", "tiles"), (v.value for v in vals)))
+    if unit is not None:
+        cap = 64
+        while True:
+            buf = (C.c_int * (4 * cap))()
+            n = lib.fp4ar_gemm_plan(M, Nn, K, sms, *[C.byref(v) for v in vals], unit, buf, cap)
+            if n < 0:
+                raise ValueError("unit out of range")
+            if n <= cap:
+                break
+            cap = n
+        out["segments"] = [tuple(buf[4 * i:4 * i + 4]) for i in range(n)]
+    return out
