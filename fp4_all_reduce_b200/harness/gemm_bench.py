@@ -41,6 +41,13 @@ def _time(fn, iters):
     return statistics.median(ts)
 
 
+def _plan(M: int, Nn: int, K: int) -> dict:
+    """The shape the library takes for this size by itself (environment overrides of a run are not reflected)."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pl = G.gemm_plan(M, Nn, K, sms)
+    return {"pair": pl["pair"], "tile_n": pl["tile_n"], "stream_k": pl["stream_k"], "units": pl["units"], "tiles": pl["tiles"]}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ms", dest="m", default="1024,4096,16384")
@@ -64,7 +71,7 @@ def main(argv=None) -> int:
             print(json.dumps({"op": "gemm_nvfp4", "M": M, "K": K, "N": Nn, "tp": tp, "us": round(us_ours, 1),
                               "tflops": round(fl / us_ours / 1e6, 1), "frac_of_cublas_bf16": round(fl / us_ours / 1e6 / peak, 3),
                               "cublas_bf16_us": round(us_ref, 1), "cublas_tflops": round(fl / us_ref / 1e6, 1),
-                              "peak_kind": kind, "tile_n": 256, "status": G.gemm_status().code}), flush=True)
+                              "peak_kind": kind, "plan": _plan(M, Nn, K), "status": G.gemm_status().code}), flush=True)
     return 0
 
 
