@@ -12,6 +12,9 @@ Variants (each is skipped with a record saying why when its library cannot be im
                      the plain RMSNorm form)
   nccl+flashinfer    NCCL BF16 all-reduce, then FlashInfer's `gemma_fused_add_rmsnorm`
   *_norm_only        the three norm kernels alone (no communication), for scale
+  fp4ar_block_nvfp4out / nccl+vllm_norm+fp4quant
+                     the block with NVFP4 rows out for a quantised next GEMM: this package's fused kernel
+                     (`EPI_NORM_NVFP4`) against NCCL + vLLM's norm + vLLM's `scaled_fp4_quant`
 
 Only library kernels that work on LOCAL tensors are used: fused all-reduce kernels of other libraries take peer
 memory as an operand and are not run here.  The reference project's counterpart is bench/block/block_bench.py:22-43,
@@ -54,6 +57,16 @@ def _external_norms(eps: float):
     return out
 
 
+def _external_fp4_quant():
+    """(callable(x_bf16, global_scale_tensor) or None, reason): vLLM's NVFP4 quantiser of a local BF16 tensor."""
+    try:
+        from vllm import _custom_ops as vops
+
+        return (lambda x, gsc: vops.scaled_fp4_quant(x, gsc)), ""
+    except Exception as e:
+        return None, f"{type(e).__name__}: {str(e)[:120]}"
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--rows", default="1024,4096,16384")
@@ -74,6 +87,7 @@ def main(argv=None) -> int:
     ctx = Fp4ArContext(max(rows_list), device=dev)
     eps = 1e-6
     ext = _external_norms(eps)
+    fp4q, fp4q_why = _external_fp4_quant()
     records = []
 
     def emit(r):
@@ -102,6 +116,22 @@ def main(argv=None) -> int:
             "nccl+fp4ar_norm": lambda i: codec.add_rmsnorm(ar(i), res, w, inplace_residual=True, out=out),
             "fp4ar_norm_only": lambda i: codec.add_rmsnorm(xs[i % nsets], res, w, inplace_residual=True, out=out),
         }
+        outq = torch.empty(rows, N.QROW_BYTES, dtype=torch.uint8, device=dev)
+        qscale = 168.0                            # 448 * 6 / 16: activations of the order of 16 use the full range
+        variants["fp4ar_block_nvfp4out"] = lambda i: ctx.all_reduce_add_rms_norm(
+            xs[i % nsets], res, w, epilogue=N.EPI_NORM_NVFP4, qscale=qscale, out=outq)
+        vnorm = ext.get("vllm_norm", (None, "vLLM norm unavailable"))[0]
+        if fp4q is not None and vnorm is not None:
+            gsc = torch.full((1,), qscale, dtype=torch.float32, device=dev)
+
+            def vllm_chain(i, vnorm=vnorm):
+                t = ar(i)
+                vnorm(t, res, w1, w)               # in place: t = norm(t + res), res = t + res
+                return fp4q(t, gsc)
+            variants["nccl+vllm_norm+fp4quant"] = vllm_chain
+        else:
+            emit({"kind": "timing", "variant": "nccl+vllm_norm+fp4quant", "tp": world, "rows": rows,
+                  "skipped": fp4q_why or "vLLM norm unavailable"})
         for name, (fn, why) in ext.items():
             if fn is None:
                 emit({"kind": "timing", "variant": "nccl+" + name, "tp": world, "rows": rows, "skipped": why})
@@ -123,7 +153,7 @@ def main(argv=None) -> int:
                 continue
             c = clk.summary()
             emit({"kind": "timing", "variant": name, "mode": "fused", "algo": "auto", "tp": world, "rows": rows, "input": "bf16",
-                  "epilogue": 1, "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
+                  "epilogue": 2 if name in ("fp4ar_block_nvfp4out", "nccl+vllm_norm+fp4quant") else 1, "med_us": round(t["med_us"], 3), "p10_us": round(t["p10_us"], 3),
                   "p90_us": round(t["p90_us"], 3), "sm_mhz": c.get("sm_mhz"), "reasons": c.get("reasons")})
         del xs, out, scratch
         torch.cuda.empty_cache()
